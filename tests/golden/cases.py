@@ -1,0 +1,86 @@
+"""Seeded input builders shared by ``make_golden.py`` (which runs the reference
+on them) and the tests (which run the oracle and the CUDA kernels on them).
+
+All randomness is ``numpy.random.default_rng(seed).standard_normal`` in fp32, a
+stream that NumPy keeps stable across versions, so the fixtures only need to
+store outputs.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+SMALL_BLOCKINGS = [
+    # name, f_tied, h_reduce, w_reduce, h, w
+    ("framewise", 1, 1, 1, 6, 8),
+    ("tied3frame", 3, 1, 1, 6, 8),
+    ("reduce2xh", 1, 2, 1, 6, 8),
+    ("reduce4xw2xh", 1, 2, 4, 6, 8),
+    ("tied3_reduce", 3, 3, 2, 6, 8),
+]
+SMALL_ITERS = (1, 2, 5)
+NOCACHE_ITERS = (1, 3)
+
+REAL_BLOCKINGS = [("framewise", 1, 1, 1), ("tied3frame", 3, 1, 1),
+                  ("reduce2xh", 1, 2, 1), ("reduce4xw2xh", 1, 2, 4)]
+
+MAP_CASES = [(1, 1, 1, 30, 52, 4680), (3, 1, 1, 30, 52, 4680), (1, 2, 1, 30, 52, 4680),
+             (1, 2, 4, 30, 52, 4680), (1, 6, 13, 30, 52, 4680), (1, 6, 4, 30, 52, 1560),
+             (3, 3, 2, 6, 8, 288), (1, 5, 4, 30, 52, 3120), (3, 2, 4, 30, 52, 9360)]
+
+
+def randn(rng, *shape):
+    return torch.from_numpy(rng.standard_normal(shape, dtype=np.float32))
+
+
+def rope_inputs():
+    """x [2, 3*5*7+4, 2, 128] (4 trailing pass-through tokens), grid (3,5,7)."""
+    rng = np.random.default_rng(101)
+    return randn(rng, 2, 3 * 5 * 7 + 4, 2, 128), (3, 5, 7)
+
+
+def cache_case(ci: int, iters: int):
+    """Small cache-path case: B=2, H=2, D=32, chunk of 3 frames written at the
+    end of a 3-chunk view of a 4-chunk buffer (so the batch stride exceeds the view)."""
+    name, ft, hr, wr, h, w = SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(1000 + 10 * ci + iters)
+    B, H, D = 2, 2, 32
+    chunk = 3 * h * w
+    n_buf, n_kv = 4 * chunk, 3 * chunk
+    q = randn(rng, B, chunk, H, D)
+    nk = randn(rng, B, chunk, H, D)
+    nv = randn(rng, B, chunk, H, D)
+    kbuf = randn(rng, B, n_buf, H, D)
+    vbuf = randn(rng, B, n_buf, H, D)
+    return dict(name=name, blocking=(ft, hr, wr, h, w), q=q, nk=nk, nv=nv, kbuf=kbuf, vbuf=vbuf,
+                start=n_kv - chunk, end=n_kv, n_kv=n_kv, sm_scale=D ** -0.5, iters=iters)
+
+
+def nocache_case(ci: int):
+    name, ft, hr, wr, h, w = SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(2000 + ci)
+    B, H, D = 1, 2, 32
+    n = 6 * h * w
+    q, k, v = randn(rng, B, n, H, D), randn(rng, B, n, H, D), randn(rng, B, n, H, D)
+    return dict(name=name, blocking=(ft, hr, wr, h, w), q=q, k=k, v=v, sm_scale=D ** -0.5,
+                block_causal=3 * h * w)
+
+
+def real_case():
+    """One head at the real block sizes: 30 x 52 grid, D=128, chunk appended to a 1-chunk cache."""
+    rng = np.random.default_rng(3000)
+    B, H, D, h, w = 1, 1, 128, 30, 52
+    chunk = 3 * h * w
+    q, nk, nv = randn(rng, B, chunk, H, D), randn(rng, B, chunk, H, D), randn(rng, B, chunk, H, D)
+    kbuf, vbuf = randn(rng, B, 2 * chunk, H, D), randn(rng, B, 2 * chunk, H, D)
+    return dict(q=q, nk=nk, nv=nv, kbuf=kbuf, vbuf=vbuf, start=chunk, end=2 * chunk, h=h, w=w,
+                sm_scale=D ** -0.5)
+
+
+def c1_case():
+    """BASELINE config 1: B=1, 12 heads, D=128, one 3-frame chunk, empty cache."""
+    rng = np.random.default_rng(0)
+    B, H, D, h, w = 1, 12, 128, 30, 52
+    chunk = 3 * h * w
+    q, k, v = randn(rng, B, chunk, H, D), randn(rng, B, chunk, H, D), randn(rng, B, chunk, H, D)
+    return dict(q=q, k=k, v=v, h=h, w=w, chunk=chunk, sm_scale=D ** -0.5)
