@@ -1,0 +1,389 @@
+#!/usr/bin/env python
+"""Benchmark of the Monarch self-attention hot path (one JSON line on stdout).
+
+A "step" is one self-attention call of one DiT layer on one 3-frame chunk at Wan-1.3B shape:
+fused RoPE + layout + in-place KV-cache write of the 4680 new tokens, then Monarch attention of
+the 4680 queries against the cache (default: framewise blocking, 7 chunks = 32760 cached tokens,
+12 heads of 128).  Inputs are seeded synthetic N(0,1) bf16 tensors.  Successive steps rotate
+through several layer caches so that every step streams its K/V from HBM, as in the real model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--blocking framewise|tied3frame|reduce2xh|reduce4xw2xh|dense] [--k 1..7]
+                    [--sweep FILE]
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs its own chunk: independent
+videos, no inter-GPU traffic on this path (weak scaling).  --impl reference times the CPU
+restatement of the reference's PyTorch path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np
+import torch
+
+BLOCKINGS = {  # name -> (f_tied, h_reduce, w_reduce)
+    "framewise": (1, 1, 1), "tied3frame": (3, 1, 1), "reduce2xh": (1, 2, 1), "reduce4xw2xh": (1, 2, 4),
+}
+H_GRID, W_GRID, HEADS, HEAD_DIM, CHUNK_FRAMES = 30, 52, 12, 128, 3
+CHUNK = CHUNK_FRAMES * H_GRID * W_GRID          # 4680 tokens
+N_LAYER_CACHES = 4                              # rotated so K/V (201 MB per layer at k=7) is never L2 resident
+
+
+def algorithmic(blocking: str, k: int, heads: int = HEADS, batch: int = 1):
+    """Algorithmic FLOPs and HBM bytes of one call (T = 1)."""
+    n_q, n_kv = CHUNK, CHUNK * k
+    if blocking == "dense":
+        flops = 4.0 * n_q * n_kv * HEAD_DIM * heads * batch
+        r_flops, l_flops = flops, 0.0
+    else:
+        ft, hr, wr = BLOCKINGS[blocking]
+        b1, b2 = ft * H_GRID // hr, W_GRID // wr
+        r_flops = 6.0 / b1 * n_q * n_kv * HEAD_DIM * heads * batch
+        l_flops = 4.0 / b2 * n_q * n_kv * HEAD_DIM * heads * batch
+        flops = r_flops + l_flops
+    bytes_ = (4 * n_q + 2 * n_kv) * heads * HEAD_DIM * 2 * batch
+    return flops, bytes_, r_flops, l_flops
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                 parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(k: int, seed: int, device, heads: int = HEADS):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    mk = lambda n: torch.randn(1, n, heads, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q, kn, vn = mk(CHUNK), mk(CHUNK), mk(CHUNK)
+    caches = []
+    for _ in range(N_LAYER_CACHES):
+        kc = torch.zeros(1, 7 * CHUNK, heads, HEAD_DIM, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        kc[:, :(k - 1) * CHUNK] = torch.randn(1, (k - 1) * CHUNK, heads, HEAD_DIM, generator=g).to(torch.bfloat16)
+        vc[:, :(k - 1) * CHUNK] = torch.randn(1, (k - 1) * CHUNK, heads, HEAD_DIM, generator=g).to(torch.bfloat16)
+        caches.append((kc.to(device), vc.to(device)))
+    return q, kn, vn, caches
+
+
+def make_step(sfb, blocking, k, q, kn, vn, caches):
+    n_kv = k * CHUNK
+    start = n_kv - CHUNK
+    start_frame = CHUNK_FRAMES * (k - 1)
+    state = {"i": 0}
+    if blocking == "dense":
+        def step(qd=q, kd=kn, vd=vn):
+            kc, vc = caches[state["i"] % len(caches)]; state["i"] += 1
+            rq = sfb.causal_rope_apply(qd, [[CHUNK_FRAMES, H_GRID, W_GRID]], None, start_frame)
+            rk = sfb.causal_rope_apply(kd, [[CHUNK_FRAMES, H_GRID, W_GRID]], None, start_frame)
+            return sfb.full_attention_with_kv_cache(rq, kc[:, :n_kv], vc[:, :n_kv], rk, vd, start, n_kv)
+    else:
+        ft, hr, wr = BLOCKINGS[blocking]
+
+        def step(qd=q, kd=kn, vd=vn):
+            kc, vc = caches[state["i"] % len(caches)]; state["i"] += 1
+            return sfb.rope_monarch_attn_with_kv_cache(qd, kd, vd, kc[:, :n_kv], vc[:, :n_kv], start, n_kv,
+                                                       start_frame, ft, hr, wr, H_GRID, W_GRID)
+    return step
+
+
+def time_steps(step, steps, warmup, dist_barrier):
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    dist_barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist_barrier()
+    return e0.elapsed_time(e1)
+
+
+def cpu_reference_step(heads_sample: int, blocking: str, k: int, seed: int = 1234):
+    """One step of the reference arithmetic on the CPU (fp32, all host threads) for
+    `heads_sample` of the heads; returns seconds."""
+    from oracle import monarch_oracle as orc
+    rng = np.random.default_rng(seed)
+    mk = lambda n: torch.from_numpy(rng.standard_normal((1, n, heads_sample, HEAD_DIM), dtype=np.float32))
+    n_kv = k * CHUNK
+    q, kn, vn = mk(CHUNK), mk(CHUNK), mk(CHUNK)
+    kc, vc = mk(n_kv), mk(n_kv)
+    t0 = time.perf_counter()
+    if blocking == "dense":
+        rq = orc.rope_apply(q, (CHUNK_FRAMES, H_GRID, W_GRID), CHUNK_FRAMES * (k - 1))
+        rk = orc.rope_apply(kn, (CHUNK_FRAMES, H_GRID, W_GRID), CHUNK_FRAMES * (k - 1))
+        kc[:, n_kv - CHUNK:] = rk; vc[:, n_kv - CHUNK:] = vn
+        orc.dense_attention(rq, kc, vc)
+    else:
+        ft, hr, wr = BLOCKINGS[blocking]
+        rq = orc.rope_apply(q, (CHUNK_FRAMES, H_GRID, W_GRID), CHUNK_FRAMES * (k - 1))
+        rk = orc.rope_apply(kn, (CHUNK_FRAMES, H_GRID, W_GRID), CHUNK_FRAMES * (k - 1))
+        orc.monarch_attn_with_kv_cache(rq, kc, vc, rk, vn, n_kv - CHUNK, n_kv, ft, hr, wr, H_GRID, W_GRID)
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    heads_sample = 4
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_step(heads_sample, args.blocking, args.k)
+    t = []
+    budget_s, t_start = 150.0, time.perf_counter()
+    for _ in range(args.steps):
+        t.append(cpu_reference_step(heads_sample, args.blocking, args.k))
+        if time.perf_counter() - t_start > budget_s:
+            break
+    sec = statistics.mean(t) * (HEADS / heads_sample)
+    fps = CHUNK_FRAMES / sec
+    flops, bytes_, _, _ = algorithmic(args.blocking, args.k)
+    line = {
+        "impl": "reference", "metric": "monarch_attn_latent_frames_per_s", "value": fps,
+        "unit": "latent frames/s (one attention layer call per 3-frame chunk)", "n_gpus": args.gpus,
+        "steps": len(t), "warmup": args.warmup, "ms_per_step": sec * 1e3, "ms_per_chunk": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": fps, "unit": "latent frames/s", "cores": cores, "kind": "port",
+                         "sample": f"{heads_sample} of {HEADS} heads per step, time scaled x{HEADS // heads_sample}; "
+                                   f"{len(t)} steps; fp32 torch CPU restatement of the reference PyTorch path"},
+        "e2e": {"value": fps, "unit": "latent frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args):
+    return {"workload": f"Wan-1.3B self-attention op, {args.blocking}, 4680-token chunk vs {args.k * CHUNK}-token "
+                        f"KV cache (k={args.k}), 12 heads x 128, B=1 per GPU, RoPE 44/42/42 fused",
+            "blocking": args.blocking, "k": args.k, "n_q": CHUNK, "n_kv": args.k * CHUNK, "heads": HEADS,
+            "head_dim": HEAD_DIM, "l2": f"{N_LAYER_CACHES} rotating layer caches "
+                                         f"({N_LAYER_CACHES * 2 * args.k * CHUNK * HEADS * HEAD_DIM * 2 / 1e6:.0f} MB) "
+                                         "> 126 MB L2, no explicit flush",
+            "parallelism": f"dp{args.gpus} (independent chunks per GPU, no collective)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--blocking", default="framewise", choices=list(BLOCKINGS) + ["dense"])
+    ap.add_argument("--k", type=int, default=7)
+    ap.add_argument("--sweep", default=None, help="also time every blocking x k and write a JSON table here")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: dist.barrier()
+    else:
+        barrier = lambda: None
+
+    import self_forcing_b200 as sfb
+    from self_forcing_b200 import _lib
+    lib = _lib.load()
+
+    q, kn, vn, caches = make_inputs(args.k, 100 + rank, device)
+    qd, kd, vd = q.to(device), kn.to(device), vn.to(device)
+    step = make_step(sfb, args.blocking, args.k, qd, kd, vd, caches)
+
+    # ---- headline: device-resident inputs -------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    n0 = lib.sfm_launch_count()
+    ms_total = time_steps(step, args.steps, args.warmup, barrier)
+    launches = (lib.sfm_launch_count() - n0) * args.steps // (args.steps + args.warmup)
+    clocks = sampler.stop()
+
+    # ---- per-kernel durations over the same steps (events around every launch) -------------
+    import ctypes as C
+    lib.sfm_profile_enable(1)
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    ms_cls = (C.c_float * 5)()
+    n_cls = (C.c_longlong * 5)()
+    _lib.check(lib.sfm_profile_read(ms_cls, n_cls, 5), "sfm_profile_read")
+    lib.sfm_profile_enable(0)
+    cls_names = ["layout_rope_cache_write", "monarch_row_step", "monarch_col_step", "monarch_iter", "dense"]
+    kernels = {cls_names[i]: {"launches_per_step": n_cls[i] / args.steps, "ms_per_step": ms_cls[i] / args.steps}
+               for i in range(5) if n_cls[i]}
+
+    # ---- end to end through the public API with host buffers --------------------------------
+    qh, kh, vh = q.pin_memory(), kn.pin_memory(), vn.pin_memory()
+    out_h = torch.empty(1, CHUNK, HEADS, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        qd2 = qh.to(device, non_blocking=True)
+        kd2 = kh.to(device, non_blocking=True)
+        vd2 = vh.to(device, non_blocking=True)
+        out = step(qd2, kd2, vd2)
+        out_h.copy_(out, non_blocking=True)
+
+    ms_e2e = time_steps(e2e_step, args.steps, args.warmup, barrier)
+
+    if use_dist:
+        t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = t.tolist()
+
+    ms_step = ms_total / args.steps
+    fps = CHUNK_FRAMES * world / (ms_step * 1e-3)
+    fps_e2e = CHUNK_FRAMES * world / (ms_e2e / args.steps * 1e-3)
+    flops, bytes_, r_flops, l_flops = algorithmic(args.blocking, args.k)
+    hbm_peak, tf_peak, peak_kind = load_peaks()
+
+    # dominant kernel = the class with the most time
+    dom = max(kernels, key=lambda n: kernels[n]["ms_per_step"]) if kernels else None
+    roofline = None
+    if dom:
+        dom_ms = kernels[dom]["ms_per_step"]
+        dom_flops = {"monarch_row_step": r_flops, "monarch_col_step": l_flops, "dense": flops}.get(dom, 0.0)
+        ach = dom_flops / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+        roofline = {"kernel": dom, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
+                    "frac": ach / tf_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "launch_ms_per_step": dom_ms,
+                    "whole_op": {"algorithmic_gflop": flops / 1e9, "algorithmic_mb": bytes_ / 1e6,
+                                 "tensor_tflops": flops / (ms_step * 1e-3) / 1e12,
+                                 "tensor_frac": flops / (ms_step * 1e-3) / 1e12 / tf_peak,
+                                 "hbm_gbs": bytes_ / (ms_step * 1e-3) / 1e9,
+                                 "hbm_frac": bytes_ / (ms_step * 1e-3) / 1e9 / hbm_peak}}
+
+    line = {
+        "metric": "monarch_attn_latent_frames_per_s", "value": fps,
+        "unit": "latent frames/s (one attention layer call per 3-frame chunk)",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "ms_per_chunk": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args),
+        "clocks": clocks,
+        "e2e": {"value": fps_e2e, "unit": "latent frames/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": 3 * q.numel() * 2, "d2h_bytes_per_step": q.numel() * 2},
+        "gpu_launches": int(launches),
+        "kernels": kernels,
+        "roofline": roofline,
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        hs = 4
+        cpu_reference_step(hs, args.blocking, args.k)
+        ts = [cpu_reference_step(hs, args.blocking, args.k) for _ in range(3)]
+        sec = statistics.median(ts) * (HEADS / hs)
+        line["cpu_baseline"] = {"value": CHUNK_FRAMES / sec, "unit": "latent frames/s", "ms_per_chunk": sec * 1e3,
+                                "cores": cores, "kind": "port",
+                                "sample": f"{hs} of {HEADS} heads, median of 3, time scaled x{HEADS // hs}; fp32 torch "
+                                          "CPU restatement of the reference PyTorch path"}
+
+    if args.sweep and rank == 0:
+        table = []
+        for blocking in list(BLOCKINGS) + ["dense"]:
+            for k in range(1, 8):
+                q2, kn2, vn2, caches2 = make_inputs(k, 7, device)
+                st = make_step(sfb, blocking, k, q2.to(device), kn2.to(device), vn2.to(device), caches2)
+                ms = time_steps(st, 20, 5, lambda: None) / 20
+                fl, by, _, _ = algorithmic(blocking, k)
+                table.append({"blocking": blocking, "k": k, "ms_per_chunk": ms, "gflop": fl / 1e9, "mb": by / 1e6,
+                              "tflops": fl / ms / 1e9, "tensor_frac": fl / ms / 1e9 / tf_peak,
+                              "hbm_gbs": by / ms / 1e6, "hbm_frac": by / ms / 1e6 / hbm_peak})
+                del caches2
+                torch.cuda.empty_cache()
+        Path(args.sweep).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.sweep).write_text(json.dumps(table, indent=1))
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if use_dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

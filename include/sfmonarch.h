@@ -1,0 +1,178 @@
+/*
+ * sfmonarch.h - C ABI of libsfmonarch.so: Monarch-structured self-attention for the
+ * causal Wan DiT's chunk-wise KV-cache rollout, hand-written CUDA for sm_100a.
+ *
+ * Every entry point takes plain pointers, sizes and a cudaStream_t (passed as void*),
+ * launches on that stream without synchronising the device, and returns an int:
+ *   0   success
+ *   <0  argument / shape / alignment / capability error (SFM_ERR_*)
+ *   >0  a cudaError_t reported by the runtime
+ * Device tensors are bf16 (uint16 storage) unless stated.  "Natural order" is the
+ * model's token order [B, N, H, D]; "Monarch order" is the block order produced by
+ * the layout map below.  The caller owns every buffer; nothing is allocated here.
+ *
+ * Each declaration names the reference interface it stands in for (paths inside the
+ * reference project).
+ */
+#ifndef SFMONARCH_H_
+#define SFMONARCH_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SFM_OK                    0
+#define SFM_ERR_NULL_POINTER     -1
+#define SFM_ERR_BAD_SHAPE        -2   /* sizes inconsistent with the blocking            */
+#define SFM_ERR_UNSUPPORTED      -3   /* head_dim != 128, b2 > 64, ...                   */
+#define SFM_ERR_ALIGNMENT        -4   /* pointers / strides must be 16-byte aligned      */
+#define SFM_ERR_WORKSPACE        -5   /* workspace too small                             */
+#define SFM_ERR_NO_DEVICE        -6   /* not an sm_100 device                            */
+#define SFM_ERR_DEVICE_STATUS    -7   /* a kernel recorded an internal error status      */
+
+/* Version of this ABI (major*100 + minor). */
+int sfm_version(void);
+
+/* Static text for a return code of this library (never NULL). */
+const char* sfm_error_string(int code);
+
+/*
+ * Blocking of an h x w token grid, shared by the calls below:
+ *   f_tied   frames tied into one Monarch group (1 = framewise, 3 = tied3frame)
+ *   h_reduce, w_reduce   split of the rows / columns of a frame into bands
+ *   h, w     token rows / columns per latent frame (30 x 52 at 480p)
+ * giving b1 = f_tied*h/h_reduce block rows, b2 = w/w_reduce block columns and
+ * h_reduce*w_reduce groups per f_tied frames.
+ */
+
+/*
+ * Token permutation between natural and Monarch order for n_tokens tokens.
+ * Host pointers; either output may be NULL.  nat2mon[n] = Monarch position of natural
+ * token n; mon2nat is the inverse.
+ * Replaces: _get_rearrange_fns (wan/modules/monarch_attn.py:1696-1703).
+ */
+int sfm_build_maps(int32_t* nat2mon, int32_t* mon2nat, int n_tokens,
+                   int f_tied, int h_reduce, int w_reduce, int h, int w);
+
+/*
+ * Rotary table on the HOST: out[pos][m] = {cos, sin} (fp32, from fp64 angles) for
+ * pos < max_len and pair m < head_dim/2; pairs are split frame/row/column as
+ * (c-2*(c/3), c/3, c/3) with c = head_dim/2, axis with p pairs using
+ * pos * theta^(-m'/p).  out holds max_len*head_dim floats.
+ * Replaces: rope_params (wan/modules/model.py:421-428) as assembled at
+ * wan/modules/causal_model.py:1352-1357.
+ */
+int sfm_rope_table(float* out, int head_dim, int max_len, double theta);
+
+/*
+ * Fused 3-axis RoPE + layout + in-place KV-cache write (one pass, 16-byte accesses).
+ *   q, k, v      [B, n_new, H, D] natural order, contiguous; q may be NULL
+ *   q_out        [B, n_new, H, D] natural order: rotated q (ignored when q is NULL)
+ *   k_cache, v_cache   [B, >= start_idx+n_new, H, D], batch stride cache_batch_stride
+ *                (elements); tokens [start_idx, start_idx+n_new) are overwritten with
+ *                rotated k and v, in Monarch order when monarch_order != 0, else natural
+ *   rope         device table from sfm_rope_table (max_len 1024), or NULL: no rotation
+ *                (inputs already rotated); frame position = start_frame + frame index,
+ *                the chunk being a (n_new/(h*w)) x h x w grid
+ * Replaces: causal_rope_apply (wan/modules/causal_model.py:687-715), the einops
+ * permutes and slice assignment of monarch_attn_with_kv_cache
+ * (wan/modules/monarch_attn.py:1782-1785, 1230-1231) and the natural-order cache write
+ * of the dense branch (wan/modules/causal_model.py:961-962).
+ */
+int sfm_rope_cache_write(const void* q, const void* k, const void* v, void* q_out,
+                         void* k_cache, void* v_cache, int64_t cache_batch_stride,
+                         const float* rope, int B, int n_new, int H, int D,
+                         int start_idx, int f_tied, int h_reduce, int w_reduce, int h, int w,
+                         int start_frame, int monarch_order, void* stream);
+
+/*
+ * Stand-alone 3-axis RoPE of one tensor x [B, L, H, D] -> out (same shape): the first
+ * frames*h*w tokens are rotated as a frames x h x w grid whose frame positions start at
+ * start_frame; the rest are copied.  rope = device table from sfm_rope_table.
+ * Replaces: causal_rope_apply (wan/modules/causal_model.py:687-715).
+ */
+int sfm_rope_apply(const void* x, void* out, const float* rope, int B, int L, int H, int D,
+                   int frames, int h, int w, int start_frame, void* stream);
+
+/*
+ * Scratch bytes sfm_monarch_fwd needs for these sizes.  The row-step results (aL, Y,
+ * cL) of one chunk of (batch, head, query-group) live there between the two kernels;
+ * bridge_budget_bytes bounds one chunk so that it stays L2 resident (0 = default).
+ * Replaces: the aL / y / cL scratch tensors of _attention_with_cache.forward
+ * (wan/modules/monarch_attn.py:1246-1259).
+ */
+size_t sfm_monarch_workspace_bytes(int B, int H, int D, int n_q, int n_kv,
+                                   int f_tied, int h_reduce, int w_reduce, int h, int w,
+                                   int num_iters, size_t bridge_budget_bytes);
+
+/*
+ * Monarch attention forward over a KV cache that already holds the new chunk.
+ *   q        [B, n_q, H, D] natural order (rotated), batch stride q_batch_stride
+ *   k_cache, v_cache  [B, n_kv, H, D] Monarch order, batch stride cache_batch_stride
+ *   out      [B, n_q, H, D] natural order, contiguous
+ *   num_iters  1 = single row/column pass; >1 = alternating updates with the
+ *              min(1/(cR+1e-6), 1e4) multiplier of the reference's iterative path
+ * Every query group attends every cached group (causality = cache extent).
+ * Replaces: _attention_with_cache.forward and its two Triton kernels
+ * (wan/modules/monarch_attn.py:1227-1323, 109-253, 698-842), monarch_attn_slow
+ * (wan/modules/monarch_attn.py:1705-1751) and return_fn (:1702).
+ */
+int sfm_monarch_fwd(const void* q, int64_t q_batch_stride,
+                    const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
+                    void* out, void* workspace, size_t workspace_bytes,
+                    int B, int H, int D, int n_q, int n_kv,
+                    int f_tied, int h_reduce, int w_reduce, int h, int w,
+                    float sm_scale, int num_iters, size_t bridge_budget_bytes, void* stream);
+
+/*
+ * Block-causal Monarch attention without a cache: q, k, v [B, N, H, D] natural order,
+ * contiguous.  Query groups of causal block c attend the key groups of blocks 0..c;
+ * causal_groups = groups per causal block (0 = no mask).  k_mon / v_mon are scratch
+ * [B, N, H, D] that receive k, v in Monarch order.
+ * Replaces: monarch_attn / _attention_no_cache.forward
+ * (wan/modules/monarch_attn.py:1753-1776, 1472-1563).
+ */
+int sfm_monarch_nocache_fwd(const void* q, const void* k, const void* v,
+                            void* k_mon, void* v_mon, void* out,
+                            void* workspace, size_t workspace_bytes,
+                            int B, int H, int D, int N,
+                            int f_tied, int h_reduce, int w_reduce, int h, int w,
+                            float sm_scale, int causal_groups, int num_iters,
+                            size_t bridge_budget_bytes, void* stream);
+
+/*
+ * Dense softmax attention, no mask: out = softmax(q k^T * scale) v.
+ *   q [B, n_q, H, D] batch stride q_batch_stride; k, v [B, n_kv, H, D] batch stride
+ *   kv_batch_stride; out [B, n_q, H, D] contiguous.
+ * Replaces: attention / flash_attention (wan/modules/attention.py:34-187) as called
+ * for the dense-init chunk and the regular configuration
+ * (wan/modules/causal_model.py:963-967).
+ */
+int sfm_dense_fwd(const void* q, int64_t q_batch_stride,
+                  const void* k, const void* v, int64_t kv_batch_stride,
+                  void* out, int B, int H, int D, int n_q, int n_kv,
+                  float sm_scale, void* stream);
+
+/*
+ * Launch accounting and optional per-kernel timing.  Kernel classes: 0 layout / RoPE /
+ * cache write, 1 Monarch row step, 2 Monarch column step, 3 Monarch iteration update,
+ * 4 dense attention (SFM_NUM_KERNEL_CLASSES of them).
+ *   sfm_launch_count    kernels this library has launched in this process
+ *   sfm_profile_enable  when on, each launch is bracketed by CUDA events on its stream
+ *   sfm_profile_read    waits for the recorded events, returns per-class total milliseconds
+ *                       and launch counts since the previous read, and forgets them
+ * Replaces: the CUDA-event profiling of CausalInferencePipeline.inference(profile=True)
+ * (pipeline/causal_inference.py:104-115, 247-281), at kernel granularity.
+ */
+#define SFM_NUM_KERNEL_CLASSES 5
+long long sfm_launch_count(void);
+int sfm_profile_enable(int on);
+int sfm_profile_read(float* ms, long long* launches, int n_classes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SFMONARCH_H_ */

@@ -1,0 +1,251 @@
+// extern "C" entry points for the Monarch forward and their host-side planning.
+#include <algorithm>
+#include <cstdlib>
+
+#include "monarch_params.cuh"
+
+using namespace sfm;
+
+namespace {
+
+constexpr size_t kDefaultBridgeBudget = 64ull << 20;   // bytes of row-step results kept per chunk
+
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// How one call is cut into chunks and how the workspace is laid out.
+struct Plan {
+    Blocking blk;
+    int A, F, n_keys;
+    int nbh_chunk, na_chunk, na_cta;
+    size_t off_aL, off_Y, off_cL, off_lse, off_aR, off_cR, total;
+};
+
+int make_plan(Plan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce, int h,
+              int w, int num_iters, size_t budget) {
+    if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
+    if (B <= 0 || H <= 0 || n_q <= 0 || n_kv <= 0 || num_iters < 1) return SFM_ERR_BAD_SHAPE;
+    int rc = make_blocking(&pl->blk, f_tied, h_reduce, w_reduce, h, w);
+    if (rc) return rc;
+    const Blocking& blk = pl->blk;
+    if (blk.b2 > kB2Max) return SFM_ERR_UNSUPPORTED;
+    if (n_q % blk.tied_tokens) return SFM_ERR_BAD_SHAPE;
+    const int group_tokens = blk.b1 * blk.b2;
+    if (n_kv % group_tokens) return SFM_ERR_BAD_SHAPE;
+    if (num_iters > 1 && blk.b1 > kIterMaxB1) return SFM_ERR_UNSUPPORTED;
+    pl->A = n_q / group_tokens;
+    pl->F = n_kv / group_tokens;
+    pl->n_keys = pl->F * blk.b1;
+    if (budget == 0) {
+        budget = kDefaultBridgeBudget;
+        if (const char* e = getenv("SFM_BRIDGE_MB")) {
+            long mb = atol(e);
+            if (mb > 0) budget = (size_t)mb << 20;
+        }
+    }
+    const size_t per_a = (size_t)blk.b2 * pl->n_keys * (2 * kHeadDim * 2 + 4) * (num_iters > 1 ? 2 : 1);
+    const int BH = B * H;
+    pl->na_cta = std::max(1, std::min(pl->A, kRMaxRows / blk.b2));
+    if (per_a * pl->A <= budget) {
+        pl->na_chunk = pl->A;
+        pl->nbh_chunk = (int)std::min<size_t>((size_t)BH, std::max<size_t>(1, budget / (per_a * pl->A)));
+    } else {
+        pl->nbh_chunk = 1;
+        int na = (int)std::max<size_t>(1, std::min<size_t>((size_t)pl->A, budget / per_a));
+        if (na >= pl->na_cta) na -= na % pl->na_cta;
+        pl->na_chunk = na;
+    }
+    const size_t aj = (size_t)pl->nbh_chunk * pl->na_chunk * blk.b2;
+    size_t off = 0;
+    pl->off_aL = off; off = align256(off + aj * pl->n_keys * kHeadDim * 2);
+    pl->off_Y = off;  off = align256(off + aj * pl->n_keys * kHeadDim * 2);
+    pl->off_cL = off; off = align256(off + aj * pl->n_keys * 4);
+    pl->off_lse = pl->off_aR = pl->off_cR = off;
+    if (num_iters > 1) {
+        pl->off_lse = off; off = align256(off + aj * blk.b1 * 4);
+        pl->off_aR = off;  off = align256(off + aj * pl->n_keys * kHeadDim * 2);
+        pl->off_cR = off;  off = align256(off + aj * pl->n_keys * 4);
+    }
+    pl->total = off;
+    return SFM_OK;
+}
+
+int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int64_t c_bs, void* out, void* ws,
+                size_t ws_bytes, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce,
+                int h, int w, float sm_scale, int num_iters, int causal_groups, size_t budget, cudaStream_t stream) {
+    if (!q || !kc || !vc || !out || !ws) return SFM_ERR_NULL_POINTER;
+    Plan pl;
+    int rc = make_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters, budget);
+    if (rc) return rc;
+    if (ws_bytes < pl.total) return SFM_ERR_WORKSPACE;
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (mis(q) || mis(kc) || mis(vc) || mis(out) || (reinterpret_cast<uintptr_t>(ws) & 255) || (q_bs % 8) || (c_bs % 8))
+        return SFM_ERR_ALIGNMENT;
+    if (causal_groups < 0 || (causal_groups > 0 && num_iters != 1)) return SFM_ERR_UNSUPPORTED;
+
+    MonarchParams p;
+    p.q = (const __nv_bfloat16*)q; p.q_bs = q_bs;
+    p.kc = (const __nv_bfloat16*)kc; p.vc = (const __nv_bfloat16*)vc; p.c_bs = c_bs;
+    p.out = (__nv_bfloat16*)out;
+    unsigned char* base = (unsigned char*)ws;
+    p.aL = (__nv_bfloat16*)(base + pl.off_aL);
+    p.Y = (__nv_bfloat16*)(base + pl.off_Y);
+    p.cL = (float*)(base + pl.off_cL);
+    p.lse = (float*)(base + pl.off_lse);
+    p.aR = (__nv_bfloat16*)(base + pl.off_aR);
+    p.cR = (float*)(base + pl.off_cR);
+    p.H = H; p.n_q = n_q; p.A = pl.A; p.F = pl.F; p.n_keys = pl.n_keys;
+    p.na_cta = pl.na_cta;
+    p.causal_groups = causal_groups;
+    p.scale = sm_scale;
+    p.blk = pl.blk;
+
+    const int BH = B * H;
+    for (int bh0 = 0; bh0 < BH; bh0 += pl.nbh_chunk) {
+        p.bh0 = bh0; p.nbh = std::min(pl.nbh_chunk, BH - bh0);
+        for (int a0 = 0; a0 < pl.A; a0 += pl.na_chunk) {
+            p.a0 = a0; p.na = std::min(pl.na_chunk, pl.A - a0);
+            // enough row-step CTAs to fill the GPU about twice over
+            int asubs = (p.na + p.na_cta - 1) / p.na_cta;
+            int base_ctas = pl.blk.b1 * asubs * p.nbh;
+            int fsplit = std::max(1, std::min(pl.F, (2 * 148 + base_ctas - 1) / base_ctas));
+            p.f_per = (pl.F + fsplit - 1) / fsplit;
+            p.fsplit = (pl.F + p.f_per - 1) / p.f_per;
+
+            for (int it = 0; it < num_iters; ++it) {
+                const bool last = it == num_iters - 1;
+                p.use_aR = it > 0;
+                p.write_Y = last;
+                p.mult0 = num_iters > 1 ? sm_scale * (1.0f / (1.0f + 1e-6f)) : sm_scale;
+                if ((rc = launch_r_step(p, stream))) return rc;
+                if (last) {
+                    if ((rc = launch_l_step(p, 0, stream))) return rc;
+                } else {
+                    if ((rc = launch_l_step(p, 1, stream))) return rc;
+                    if ((rc = launch_l_iter(p, stream))) return rc;
+                }
+            }
+        }
+    }
+    return SFM_OK;
+}
+
+}  // namespace
+
+extern "C" int sfm_version(void) { return 100; }
+
+extern "C" const char* sfm_error_string(int code) {
+    switch (code) {
+        case SFM_OK: return "success";
+        case SFM_ERR_NULL_POINTER: return "null pointer argument";
+        case SFM_ERR_BAD_SHAPE: return "sizes inconsistent with the blocking";
+        case SFM_ERR_UNSUPPORTED: return "unsupported size (head_dim must be 128, block columns <= 64)";
+        case SFM_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+        case SFM_ERR_WORKSPACE: return "workspace too small";
+        case SFM_ERR_NO_DEVICE: return "no sm_100 device";
+        case SFM_ERR_DEVICE_STATUS: return "kernel recorded an internal error status";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "unknown error";
+}
+
+extern "C" size_t sfm_monarch_workspace_bytes(int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce,
+                                              int w_reduce, int h, int w, int num_iters, size_t bridge_budget_bytes) {
+    Plan pl;
+    if (make_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters, bridge_budget_bytes)) return 0;
+    return pl.total;
+}
+
+extern "C" int sfm_monarch_fwd(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                               int64_t cache_batch_stride, void* out, void* workspace, size_t workspace_bytes, int B,
+                               int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce, int h, int w,
+                               float sm_scale, int num_iters, size_t bridge_budget_bytes, void* stream) {
+    return run_monarch(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, out, workspace, workspace_bytes, B, H,
+                       D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters, 0, bridge_budget_bytes,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int sfm_monarch_nocache_fwd(const void* q, const void* k, const void* v, void* k_mon, void* v_mon,
+                                       void* out, void* workspace, size_t workspace_bytes, int B, int H, int D, int N,
+                                       int f_tied, int h_reduce, int w_reduce, int h, int w, float sm_scale,
+                                       int causal_groups, int num_iters, size_t bridge_budget_bytes, void* stream) {
+    if (!k_mon || !v_mon) return SFM_ERR_NULL_POINTER;
+    int rc = sfm_rope_cache_write(nullptr, k, v, nullptr, k_mon, v_mon, (int64_t)N * H * D, nullptr, B, N, H, D, 0,
+                                  f_tied, h_reduce, w_reduce, h, w, 0, 1, stream);
+    if (rc) return rc;
+    return run_monarch(q, (int64_t)N * H * D, k_mon, v_mon, (int64_t)N * H * D, out, workspace, workspace_bytes, B, H,
+                       D, N, N, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters, causal_groups,
+                       bridge_budget_bytes, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// launch accounting / per-kernel timing
+// ---------------------------------------------------------------------------------------------
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "profile.cuh"
+
+namespace {
+std::atomic<long long> g_launches[kNumClasses];
+std::atomic<int> g_profile_on{0};
+struct EventPair { int cls; cudaEvent_t start, stop; };
+std::mutex g_prof_mutex;
+std::vector<EventPair> g_pairs;       // recorded since the last read
+std::vector<EventPair> g_free_pairs;  // recycled events
+}  // namespace
+
+namespace sfm {
+LaunchScope::LaunchScope(int cls, cudaStream_t stream) : cls_(cls), stream_(stream), slot_(-1) {
+    g_launches[cls].fetch_add(1, std::memory_order_relaxed);
+    if (!g_profile_on.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    EventPair ep;
+    if (!g_free_pairs.empty()) {
+        ep = g_free_pairs.back();
+        g_free_pairs.pop_back();
+    } else {
+        if (cudaEventCreate(&ep.start) != cudaSuccess || cudaEventCreate(&ep.stop) != cudaSuccess) return;
+    }
+    ep.cls = cls;
+    cudaEventRecord(ep.start, stream);
+    g_pairs.push_back(ep);
+    slot_ = (int)g_pairs.size() - 1;
+}
+LaunchScope::~LaunchScope() {
+    if (slot_ < 0) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (slot_ < (int)g_pairs.size()) cudaEventRecord(g_pairs[slot_].stop, stream_);
+}
+}  // namespace sfm
+
+extern "C" long long sfm_launch_count(void) {
+    long long n = 0;
+    for (int c = 0; c < kNumClasses; ++c) n += g_launches[c].load();
+    return n;
+}
+
+extern "C" int sfm_profile_enable(int on) {
+    g_profile_on.store(on ? 1 : 0);
+    return SFM_OK;
+}
+
+extern "C" int sfm_profile_read(float* ms, long long* launches, int n_classes) {
+    if (!ms || !launches) return SFM_ERR_NULL_POINTER;
+    if (n_classes != kNumClasses) return SFM_ERR_BAD_SHAPE;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    for (int c = 0; c < kNumClasses; ++c) { ms[c] = 0.f; launches[c] = 0; }
+    for (auto& ep : g_pairs) {
+        cudaError_t e = cudaEventSynchronize(ep.stop);
+        if (e != cudaSuccess) return (int)e;
+        float t = 0.f;
+        e = cudaEventElapsedTime(&t, ep.start, ep.stop);
+        if (e != cudaSuccess) return (int)e;
+        ms[ep.cls] += t;
+        launches[ep.cls] += 1;
+        g_free_pairs.push_back(ep);
+    }
+    g_pairs.clear();
+    return SFM_OK;
+}

@@ -1,0 +1,187 @@
+// Layout maps, rotary table and the fused RoPE + layout + in-place KV-cache write kernel.
+#include <math.h>
+
+#include "common.cuh"
+#include "profile.cuh"
+
+namespace sfm {
+
+// One thread moves one 16-byte vector (8 bf16 = 4 rotary pairs) of one (token, head) row of q, k
+// and v.  Reads and writes are 16-byte vectors; a warp covers two full 256-byte rows per tensor.
+// The kernel is HBM bound: it reads 3 tensors and writes 3 (2 when q is absent).
+__global__ void __launch_bounds__(256)
+rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k, const uint4* __restrict__ v,
+                        uint4* __restrict__ q_out, uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
+                        long long cache_batch_stride_vec, const float2* __restrict__ rope,
+                        int B, int n_new, int H, int start_idx, Blocking blk, int start_frame,
+                        int monarch_order, int p0, int p1) {
+    constexpr int kVecPerRow = kHeadDim / 8;  // 16
+    const long long total = (long long)B * n_new * H * kVecPerRow;
+    const int frame_tokens = blk.h * blk.w;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        int vec = (int)(idx % kVecPerRow);
+        long long row = idx / kVecPerRow;  // (b, n, h)
+        int hd = (int)(row % H);
+        long long bn = row / H;
+        int n = (int)(bn % n_new);
+        int b = (int)(bn / n_new);
+
+        uint4 kv = k[idx];
+        uint4 vv = v[idx];
+        uint4 qv = make_uint4(0, 0, 0, 0);
+        if (q) qv = q[idx];
+
+        if (rope) {
+            int fr = n / frame_tokens, rem = n - fr * frame_tokens;
+            int rw = rem / blk.w, cl = rem - rw * blk.w;
+            int pos_f = start_frame + fr;
+            uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
+            uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                int m = vec * 4 + p;  // rotary pair index within the head
+                int pos = m < p0 ? pos_f : (m < p0 + p1 ? rw : cl);
+                float2 cs = rope[pos * (kHeadDim / 2) + m];
+                {
+                    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&kw[p]);
+                    float re = __low2float(x), im = __high2float(x);
+                    kw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
+                }
+                if (q) {
+                    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&qw[p]);
+                    float re = __low2float(x), im = __high2float(x);
+                    qw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
+                }
+            }
+        }
+        if (q) q_out[idx] = qv;
+        int dst_tok = start_idx + (monarch_order ? blk.nat2mon(n) : n);
+        long long dst = (long long)b * cache_batch_stride_vec + ((long long)dst_tok * H + hd) * kVecPerRow + vec;
+        k_cache[dst] = kv;
+        v_cache[dst] = vv;
+    }
+}
+
+}  // namespace sfm
+
+using namespace sfm;
+
+extern "C" int sfm_build_maps(int32_t* nat2mon, int32_t* mon2nat, int n_tokens, int f_tied, int h_reduce,
+                              int w_reduce, int h, int w) {
+    Blocking blk;
+    int rc = make_blocking(&blk, f_tied, h_reduce, w_reduce, h, w);
+    if (rc) return rc;
+    if (n_tokens <= 0 || n_tokens % blk.tied_tokens) return SFM_ERR_BAD_SHAPE;
+    for (int n = 0; n < n_tokens; ++n) {
+        int m = blk.nat2mon(n);
+        if (nat2mon) nat2mon[n] = m;
+        if (mon2nat) mon2nat[m] = n;
+    }
+    return SFM_OK;
+}
+
+extern "C" int sfm_rope_table(float* out, int head_dim, int max_len, double theta) {
+    if (!out) return SFM_ERR_NULL_POINTER;
+    if (head_dim <= 0 || head_dim % 2 || max_len <= 0) return SFM_ERR_BAD_SHAPE;
+    int c = head_dim / 2;
+    int split[3] = {c - 2 * (c / 3), c / 3, c / 3};
+    for (int pos = 0; pos < max_len; ++pos) {
+        int m = 0;
+        for (int ax = 0; ax < 3; ++ax) {
+            for (int mm = 0; mm < split[ax]; ++mm, ++m) {
+                double inv = 1.0 / pow(theta, (double)(2 * mm) / (double)(2 * split[ax]));
+                double ang = (double)pos * inv;
+                out[((size_t)pos * c + m) * 2 + 0] = (float)cos(ang);
+                out[((size_t)pos * c + m) * 2 + 1] = (float)sin(ang);
+            }
+        }
+    }
+    return SFM_OK;
+}
+
+extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v, void* q_out, void* k_cache,
+                                    void* v_cache, int64_t cache_batch_stride, const float* rope, int B,
+                                    int n_new, int H, int D, int start_idx, int f_tied, int h_reduce,
+                                    int w_reduce, int h, int w, int start_frame, int monarch_order,
+                                    void* stream) {
+    if (!k || !v || !k_cache || !v_cache) return SFM_ERR_NULL_POINTER;
+    if (q && !q_out) return SFM_ERR_NULL_POINTER;
+    if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
+    Blocking blk;
+    int rc = make_blocking(&blk, f_tied, h_reduce, w_reduce, h, w);
+    if (rc) return rc;
+    if (B <= 0 || H <= 0 || n_new <= 0 || start_idx < 0) return SFM_ERR_BAD_SHAPE;
+    if (monarch_order && n_new % blk.tied_tokens) return SFM_ERR_BAD_SHAPE;
+    if (rope) {
+        if (n_new % (h * w)) return SFM_ERR_BAD_SHAPE;
+        if (start_frame < 0 || start_frame + n_new / (h * w) > 1024 || h > 1024 || w > 1024) return SFM_ERR_BAD_SHAPE;
+    }
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (mis(q) || mis(k) || mis(v) || mis(q_out) || mis(k_cache) || mis(v_cache) || (cache_batch_stride % 8))
+        return SFM_ERR_ALIGNMENT;
+    if (cache_batch_stride < (int64_t)(start_idx + n_new) * H * D && B > 1) return SFM_ERR_BAD_SHAPE;
+    int c = D / 2;
+    int p0 = c - 2 * (c / 3), p1 = c / 3;
+    long long total = (long long)B * n_new * H * (D / 8);
+    int threads = 256;
+    long long want = (total + threads - 1) / threads;
+    int blocks = (int)(want < 148LL * 16 ? want : 148LL * 16);  // grid-stride; 16 resident CTAs per SM
+    LaunchScope scope(kClsLayout, (cudaStream_t)stream);
+    rope_cache_write_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
+        (const uint4*)q, (const uint4*)k, (const uint4*)v, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache,
+        cache_batch_stride / 8, (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0,
+        p1);
+    return (int)cudaGetLastError();
+}
+
+namespace sfm {
+// Stand-alone rotation of one tensor (same arithmetic as the fused kernel above).
+__global__ void __launch_bounds__(256)
+rope_apply_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, const float2* __restrict__ rope, int B,
+                  int L, int H, int seq, int hgrid, int wgrid, int start_frame, int p0, int p1) {
+    constexpr int kVecPerRow = kHeadDim / 8;
+    const long long total = (long long)B * L * H * kVecPerRow;
+    const int frame_tokens = hgrid * wgrid;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        int vec = (int)(idx % kVecPerRow);
+        long long row = idx / kVecPerRow;
+        int n = (int)((row / H) % L);
+        uint4 xv = x[idx];
+        if (n < seq) {
+            int fr = n / frame_tokens, rem = n - fr * frame_tokens;
+            int rw = rem / wgrid, cl = rem - rw * wgrid;
+            uint32_t* xw = reinterpret_cast<uint32_t*>(&xv);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                int m = vec * 4 + p;
+                int pos = m < p0 ? start_frame + fr : (m < p0 + p1 ? rw : cl);
+                float2 cs = rope[pos * (kHeadDim / 2) + m];
+                __nv_bfloat162 v2 = *reinterpret_cast<__nv_bfloat162*>(&xw[p]);
+                float re = __low2float(v2), im = __high2float(v2);
+                xw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
+            }
+        }
+        out[idx] = xv;
+    }
+}
+}  // namespace sfm
+
+extern "C" int sfm_rope_apply(const void* x, void* out, const float* rope, int B, int L, int H, int D, int frames,
+                              int h, int w, int start_frame, void* stream) {
+    if (!x || !out || !rope) return SFM_ERR_NULL_POINTER;
+    if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
+    if (B <= 0 || L <= 0 || H <= 0 || frames <= 0 || h <= 0 || w <= 0) return SFM_ERR_BAD_SHAPE;
+    if ((long long)frames * h * w > L) return SFM_ERR_BAD_SHAPE;
+    if (start_frame < 0 || start_frame + frames > 1024 || h > 1024 || w > 1024) return SFM_ERR_BAD_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return SFM_ERR_ALIGNMENT;
+    int c = D / 2, p0 = c - 2 * (c / 3), p1 = c / 3;
+    long long total = (long long)B * L * H * (D / 8);
+    long long want = (total + 255) / 256;
+    int blocks = (int)(want < 148LL * 16 ? want : 148LL * 16);
+    LaunchScope scope(kClsLayout, (cudaStream_t)stream);
+    rope_apply_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)out, (const float2*)rope, B,
+                                                                 L, H, frames * h * w, h, w, start_frame, p0, p1);
+    return (int)cudaGetLastError();
+}

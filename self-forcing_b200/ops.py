@@ -1,0 +1,302 @@
+"""Attention operators with the reference's call signatures, backed by libsfmonarch.so.
+
+Every function here launches hand-written sm_100a kernels through the C ABI on the current
+CUDA stream.  Inputs must be CUDA bf16 tensors with head_dim 128; anything else raises (there
+is no eager / CPU fallback).  Scratch memory is a per-device buffer that grows on demand and
+is reused by later calls on the same stream order (the reference is single-stream too).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_workspaces: Dict[Tuple[int, str], torch.Tensor] = {}
+_rope_tables: Dict[tuple, torch.Tensor] = {}
+
+
+# ------------------------------------------------------------------------------------- helpers
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _require(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+    if t.dim() != 4 or t.shape[-1] != 128:
+        raise ValueError(f"{name} must be [B, N, H, 128], got {tuple(t.shape)}")
+
+
+def _token_major(t: torch.Tensor) -> bool:
+    """[B, N, H, D] with dense (N, H, D) strides; the batch stride is free."""
+    _, n, h, d = t.shape
+    return t.stride(3) == 1 and t.stride(2) == d and (n == 1 or t.stride(1) == h * d)
+
+
+def _as_token_major(t: torch.Tensor) -> torch.Tensor:
+    return t if _token_major(t) else t.contiguous()
+
+
+def _batch_stride(t: torch.Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 else t.shape[1] * t.shape[2] * t.shape[3]
+
+
+def _workspace(device: torch.device, nbytes: int, tag: str = "monarch") -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), tag)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _rope_table_from_freqs(freqs: Optional[torch.Tensor], device: torch.device) -> torch.Tensor:
+    """Device table [1024, 64, 2] fp32 = (cos, sin).  Built from the model's complex128
+    ``freqs`` buffer when given (causal_model.py:1352-1357), else by the library."""
+    if freqs is None:
+        key = ("lib", device)
+        tab = _rope_tables.get(key)
+        if tab is None:
+            host = np.empty((1024, 64, 2), dtype=np.float32)
+            _lib.check(_lib.load().sfm_rope_table(host.ctypes.data_as(C.c_void_p), 128, 1024, 10000.0),
+                       "sfm_rope_table")
+            tab = torch.from_numpy(host).to(device)
+            _rope_tables[key] = tab
+        return tab
+    key = (freqs.data_ptr(), tuple(freqs.shape), device)
+    tab = _rope_tables.get(key)
+    if tab is None:
+        if freqs.dim() != 2 or freqs.shape[1] != 64 or freqs.shape[0] < 1024 or not freqs.is_complex():
+            raise ValueError("freqs must be a complex [>=1024, 64] table")
+        tab = torch.view_as_real(freqs[:1024].to(torch.complex128)).to(torch.float32).contiguous().to(device)
+        _rope_tables[key] = tab
+    return tab
+
+
+def workspace_bytes(B, H, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters=1, bridge_budget_bytes=0) -> int:
+    return int(_lib.load().sfm_monarch_workspace_bytes(B, H, 128, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w,
+                                                       num_iters, bridge_budget_bytes))
+
+
+def build_maps(n_tokens, f_tied, h_reduce, w_reduce, h, w):
+    """(nat2mon, mon2nat) int32 arrays: the token permutation of
+    _get_rearrange_fns (monarch_attn.py:1696-1703)."""
+    a = np.empty(n_tokens, dtype=np.int32)
+    b = np.empty(n_tokens, dtype=np.int32)
+    _lib.check(_lib.load().sfm_build_maps(a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), n_tokens,
+                                          f_tied, h_reduce, w_reduce, h, w), "sfm_build_maps")
+    return a, b
+
+
+def _cache_view_ok(c: torch.Tensor, name: str) -> None:
+    _require(c, name)
+    if not _token_major(c):
+        raise ValueError(f"{name} must keep dense (token, head, dim) strides: it is written in place")
+
+
+def _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters):
+    B, n_q, H, D = q.shape
+    n_kv = k_cache.shape[1]
+    lib = _lib.load()
+    nbytes = lib.sfm_monarch_workspace_bytes(B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters, 0)
+    if nbytes == 0:
+        # let the entry point produce the precise error
+        nbytes = 256
+    ws = _workspace(q.device, nbytes)
+    out = torch.empty((B, n_q, H, D), dtype=q.dtype, device=q.device)
+    rc = lib.sfm_monarch_fwd(_ptr(q), _batch_stride(q), _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache),
+                             _ptr(out), _ptr(ws), ws.numel(), B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w,
+                             float(sm_scale), int(num_iters), 0, _stream())
+    _lib.check(rc, "sfm_monarch_fwd")
+    return out
+
+
+# ------------------------------------------------------------------------------------- public
+def monarch_attn_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end_idx, f_tied, h_reduce, w_reduce,
+                               h, w, sm_scale=None, num_iters=1, grad_only_new_kv=False):
+    """Same contract as the reference's monarch_attn_with_kv_cache (monarch_attn.py:1778-1796):
+    new_k / new_v are written, in Monarch block order, into k_cache / v_cache[:, start_idx:end_idx]
+    IN PLACE, then q attends the whole cache view.  Forward only (grad_only_new_kv is accepted
+    and ignored).  q, new_k, new_v: [B, n, H, 128] bf16 (already rotated); caches [B, n_kv, H, 128]
+    bf16, possibly a [:, :n_kv] view of a longer buffer.  Returns [B, n_q, H, 128]."""
+    del grad_only_new_kv
+    for t, name in ((q, "q"), (new_k, "new_k"), (new_v, "new_v")):
+        _require(t, name)
+    _cache_view_ok(k_cache, "k_cache")
+    _cache_view_ok(v_cache, "v_cache")
+    if k_cache.stride() != v_cache.stride() or k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must share shape and strides")
+    B, n_q, H, D = q.shape
+    n_new = new_k.shape[1]
+    if end_idx - start_idx != n_new or new_v.shape != new_k.shape or end_idx > k_cache.shape[1] or start_idx < 0:
+        raise ValueError("start_idx/end_idx do not match new_k / the cache extent")
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    q = _as_token_major(q)
+    new_k = new_k.contiguous()
+    new_v = new_v.contiguous()
+    rc = _lib.load().sfm_rope_cache_write(_ptr(None), _ptr(new_k), _ptr(new_v), _ptr(None), _ptr(k_cache),
+                                          _ptr(v_cache), _batch_stride(k_cache), _ptr(None), B, n_new, H, D,
+                                          int(start_idx), f_tied, h_reduce, w_reduce, h, w, 0, 1, _stream())
+    _lib.check(rc, "sfm_rope_cache_write")
+    return _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
+
+
+def rope_monarch_attn_with_kv_cache(q, k, v, k_cache, v_cache, start_idx, end_idx, start_frame, f_tied, h_reduce,
+                                    w_reduce, h, w, freqs=None, sm_scale=None, num_iters=1):
+    """Fused front end: q, k are the UN-rotated projections.  One kernel applies the 3-axis RoPE
+    (frame positions start at start_frame), keeps rotated q, and writes rotated k and v into the
+    cache slot in Monarch order; then the Monarch forward runs.  Equivalent to
+    causal_rope_apply(q), causal_rope_apply(k) followed by monarch_attn_with_kv_cache
+    (causal_model.py:902-905, 1085-1100)."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _require(t, name)
+    _cache_view_ok(k_cache, "k_cache")
+    _cache_view_ok(v_cache, "v_cache")
+    B, n_q, H, D = q.shape
+    if end_idx - start_idx != n_q or k.shape != q.shape or v.shape != q.shape or end_idx > k_cache.shape[1]:
+        raise ValueError("start_idx/end_idx do not match the chunk / the cache extent")
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    tab = _rope_table_from_freqs(freqs, q.device)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q_rot = torch.empty_like(q)
+    rc = _lib.load().sfm_rope_cache_write(_ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(k_cache), _ptr(v_cache),
+                                          _batch_stride(k_cache), _ptr(tab), B, n_q, H, D, int(start_idx), f_tied,
+                                          h_reduce, w_reduce, h, w, int(start_frame), 1, _stream())
+    _lib.check(rc, "sfm_rope_cache_write")
+    return _monarch_fwd(q_rot, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
+
+
+def monarch_attn(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale=None, block_causal_size=None, num_iters=1):
+    """Same contract as the reference's monarch_attn (monarch_attn.py:1753-1776): no cache;
+    with block_causal_size, causal over blocks of that many tokens (forward only)."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _require(t, name)
+    B, N, H, D = q.shape
+    if k.shape != q.shape and block_causal_size is not None:
+        raise ValueError("block-causal Monarch needs kv length equal to q length")
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    lib = _lib.load()
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    n_kv = k.shape[1]
+    causal_groups = 0
+    if block_causal_size is not None:
+        b1 = f_tied * (h // h_reduce)
+        b2 = w // w_reduce
+        if N % block_causal_size or block_causal_size % (b1 * b2):
+            raise ValueError("block_causal_size must divide the sequence and align with Monarch blocks")
+        if num_iters != 1:
+            raise ValueError("causal currently only supported for num_iters=1")
+        causal_groups = block_causal_size // (b1 * b2)
+    if n_kv != N:
+        k_mon = torch.empty_like(k)
+        v_mon = torch.empty_like(v)
+        rc = lib.sfm_rope_cache_write(_ptr(None), _ptr(k), _ptr(v), _ptr(None), _ptr(k_mon), _ptr(v_mon),
+                                      n_kv * H * D, _ptr(None), B, n_kv, H, D, 0, f_tied, h_reduce, w_reduce, h, w,
+                                      0, 1, _stream())
+        _lib.check(rc, "sfm_rope_cache_write")
+        return _monarch_fwd(q, k_mon, v_mon, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
+    nbytes = lib.sfm_monarch_workspace_bytes(B, H, D, N, N, f_tied, h_reduce, w_reduce, h, w, num_iters, 0) or 256
+    ws = _workspace(q.device, nbytes)
+    out = torch.empty_like(q)
+    k_mon = torch.empty_like(k)
+    v_mon = torch.empty_like(v)
+    rc = lib.sfm_monarch_nocache_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(k_mon), _ptr(v_mon), _ptr(out), _ptr(ws),
+                                     ws.numel(), B, H, D, N, f_tied, h_reduce, w_reduce, h, w, float(sm_scale),
+                                     causal_groups, int(num_iters), 0, _stream())
+    _lib.check(rc, "sfm_monarch_nocache_fwd")
+    return out
+
+
+def flash_attention(q, k, v, q_lens=None, k_lens=None, dropout_p=0., softmax_scale=None, q_scale=None,
+                    causal=False, window_size=(-1, -1), deterministic=False, dtype=torch.bfloat16, version=None):
+    """Dense softmax attention with the reference's flash_attention signature
+    (wan/modules/attention.py:34-138).  Only what the causal rollout uses is supported: full
+    lengths, no dropout, no mask, no window."""
+    del deterministic, version
+    if q_lens is not None or k_lens is not None:
+        raise NotImplementedError("variable lengths are not used by the KV-cache rollout")
+    if causal or dropout_p != 0. or tuple(window_size) != (-1, -1):
+        raise NotImplementedError("only unmasked, dropout-free dense attention is implemented")
+    out_dtype = q.dtype
+    if q.dtype != torch.bfloat16:
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _require(t, name)
+    if q_scale is not None:
+        q = q * q_scale
+    B, n_q, H, D = q.shape
+    if softmax_scale is None:
+        softmax_scale = D ** -0.5
+    q = _as_token_major(q)
+    k = _as_token_major(k)
+    v = _as_token_major(v)
+    if _batch_stride(k) != _batch_stride(v):
+        v = v.contiguous()
+        k = k.contiguous()
+    out = torch.empty((B, n_q, H, D), dtype=torch.bfloat16, device=q.device)
+    rc = _lib.load().sfm_dense_fwd(_ptr(q), _batch_stride(q), _ptr(k), _ptr(v), _batch_stride(k), _ptr(out), B, H, D,
+                                   n_q, k.shape[1], float(softmax_scale), _stream())
+    _lib.check(rc, "sfm_dense_fwd")
+    return out.type(out_dtype)
+
+
+def attention(q, k, v, q_lens=None, k_lens=None, dropout_p=0., softmax_scale=None, q_scale=None, causal=False,
+              window_size=(-1, -1), deterministic=False, dtype=torch.bfloat16, fa_version=None):
+    """Same signature as the reference's attention (wan/modules/attention.py:141-187)."""
+    return flash_attention(q=q, k=k, v=v, q_lens=q_lens, k_lens=k_lens, dropout_p=dropout_p,
+                           softmax_scale=softmax_scale, q_scale=q_scale, causal=causal, window_size=window_size,
+                           deterministic=deterministic, dtype=dtype, version=fa_version)
+
+
+def full_attention_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end_idx, sm_scale=None,
+                                 grad_only_new_kv=False):
+    """Dense attention after an in-place, natural-order cache write
+    (wan/modules/attn_patch.py:416; the dense branch of causal_model.py:961-967)."""
+    del grad_only_new_kv
+    for t, name in ((q, "q"), (new_k, "new_k"), (new_v, "new_v")):
+        _require(t, name)
+    _cache_view_ok(k_cache, "k_cache")
+    _cache_view_ok(v_cache, "v_cache")
+    B, n_q, H, D = q.shape
+    n_new = new_k.shape[1]
+    if end_idx - start_idx != n_new or end_idx > k_cache.shape[1]:
+        raise ValueError("start_idx/end_idx do not match new_k / the cache extent")
+    new_k, new_v = new_k.contiguous(), new_v.contiguous()
+    rc = _lib.load().sfm_rope_cache_write(_ptr(None), _ptr(new_k), _ptr(new_v), _ptr(None), _ptr(k_cache),
+                                          _ptr(v_cache), _batch_stride(k_cache), _ptr(None), B, n_new, H, D,
+                                          int(start_idx), 1, 1, 1, 1, 1, 0, 0, _stream())
+    _lib.check(rc, "sfm_rope_cache_write")
+    return attention(q, k_cache, v_cache, softmax_scale=sm_scale)
+
+
+def causal_rope_apply(x, grid_sizes, freqs, start_frame=0):
+    """Same contract as the reference's causal_rope_apply (causal_model.py:687-715) for a batch
+    whose samples share one (frames, rows, cols) grid: rotate the first frames*rows*cols tokens,
+    pass the rest through; result in x's dtype."""
+    _require(x, "x")
+    if isinstance(grid_sizes, torch.Tensor):
+        grid_sizes = grid_sizes.tolist()
+    grids = {tuple(int(v) for v in g) for g in grid_sizes}
+    if len(grids) != 1:
+        raise NotImplementedError("all samples must share one token grid")
+    f, h, w = next(iter(grids))
+    B, L, H, D = x.shape
+    tab = _rope_table_from_freqs(freqs, x.device)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    rc = _lib.load().sfm_rope_apply(_ptr(x), _ptr(out), _ptr(tab), B, L, H, D, f, h, w, int(start_frame), _stream())
+    _lib.check(rc, "sfm_rope_apply")
+    return out

@@ -1,0 +1,105 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every declared symbol, and its
+host-only entry points (maps, rotary table, planning, argument validation) agree with the oracle."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import cases
+from oracle import monarch_oracle as orc
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def sfb():
+    import self_forcing_b200
+    return self_forcing_b200
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "sfmonarch.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sfm_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_exported_and_bound(sfb):
+    from self_forcing_b200 import _lib
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in sfmonarch.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+    assert lib.sfm_version() >= 100
+    assert lib.sfm_error_string(-2).decode().startswith("sizes")
+
+
+@pytest.mark.parametrize("case", cases.MAP_CASES)
+def test_maps_bit_exact(sfb, golden, case):
+    ft, hr, wr, h, w, n = case
+    nat2mon, mon2nat = sfb.build_maps(n, ft, hr, wr, h, w)
+    key = f"map_{ft}_{hr}_{wr}_{h}_{w}_{n}"
+    assert np.array_equal(mon2nat, golden[key + "_mon2nat"])
+    o_nat2mon, o_mon2nat = orc.token_maps(n, ft, hr, wr, h, w)
+    assert np.array_equal(nat2mon, o_nat2mon) and np.array_equal(mon2nat, o_mon2nat)
+
+
+def test_maps_reject_bad_shapes(sfb):
+    with pytest.raises(ValueError):
+        sfb.build_maps(100, 1, 1, 1, 30, 52)      # not a whole frame
+    with pytest.raises(ValueError):
+        sfb.build_maps(1560, 1, 4, 1, 30, 52)     # 4 does not divide 30
+
+
+def test_rope_table_matches_oracle(sfb):
+    from self_forcing_b200 import _lib
+    host = np.empty((1024, 64, 2), dtype=np.float32)
+    assert _lib.load().sfm_rope_table(host.ctypes.data_as(C.c_void_p), 128, 1024, 10000.0) == 0
+    cos, sin, _ = orc.rope_table(128, 1024)
+    assert np.array_equal(host[..., 0], cos.numpy().astype(np.float32))
+    assert np.array_equal(host[..., 1], sin.numpy().astype(np.float32))
+
+
+def test_workspace_planning(sfb):
+    # framewise, 7 chunks cached: the bridge of one head is 3*52 columns x 630 keys x 516 bytes
+    per_head = 3 * 52 * 630 * (2 * 128 * 2 + 4)
+    got = sfb.workspace_bytes(1, 12, 4680, 32760, 1, 1, 1, 30, 52, bridge_budget_bytes=per_head + 4096)
+    assert per_head <= got <= per_head + 3 * 256
+    got2 = sfb.workspace_bytes(1, 12, 4680, 32760, 1, 1, 1, 30, 52, bridge_budget_bytes=3 * per_head)
+    assert 3 * per_head <= got2 <= 3 * per_head + 3 * 256
+    # a budget below one query group still plans one group per chunk
+    small = sfb.workspace_bytes(1, 12, 4680, 32760, 1, 1, 1, 30, 52, bridge_budget_bytes=1 << 20)
+    assert per_head // 3 <= small <= per_head // 3 + 3 * 256
+    # invalid sizes plan to zero bytes
+    assert sfb.workspace_bytes(1, 12, 4680, 32761, 1, 1, 1, 30, 52) == 0
+    assert sfb.workspace_bytes(1, 12, 4000, 32760, 1, 1, 1, 30, 52) == 0
+
+
+def test_ops_refuse_cpu_tensors(sfb):
+    import torch
+    q = torch.zeros(1, 1560, 1, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        sfb.monarch_attn_with_kv_cache(q, q.clone(), q.clone(), q, q, 0, 1560, 1, 1, 1, 30, 52)
+    with pytest.raises(RuntimeError):
+        sfb.attention(q, q, q)
+
+
+def test_entry_points_validate_arguments_without_a_gpu(sfb):
+    """Argument checks run before any CUDA call, so they can be exercised on a CPU-only box."""
+    from self_forcing_b200 import _lib
+    lib = _lib.load()
+    null = C.c_void_p(0)
+    one = C.c_void_p(256)
+    assert lib.sfm_dense_fwd(null, 0, null, null, 0, null, 1, 1, 128, 16, 16, 1.0, null) == -1
+    assert lib.sfm_dense_fwd(one, 0, one, one, 0, one, 1, 1, 64, 16, 16, 1.0, null) == -3
+    assert lib.sfm_dense_fwd(C.c_void_p(260), 0, one, one, 0, one, 1, 1, 128, 16, 16, 1.0, null) == -4
+    assert lib.sfm_monarch_fwd(one, 0, one, one, 0, one, one, 0, 1, 1, 128, 1560, 1560, 1, 1, 1, 30, 52,
+                               1.0, 1, 0, null) == -5
+    assert lib.sfm_monarch_fwd(one, 0, one, one, 0, one, one, 1 << 30, 1, 1, 128, 1000, 1560, 1, 1, 1, 30, 52,
+                               1.0, 1, 0, null) == -2
+    assert lib.sfm_rope_cache_write(null, one, one, null, one, one, 0, null, 1, 100, 1, 128, 0, 1, 1, 1, 30, 52,
+                                    0, 1, null) == -2

@@ -1,0 +1,310 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle and the golden
+fixtures.  Tolerance for bf16 results, from the acceptance rule of the task: max-abs <= 2e-2 and
+relative L2 <= 1e-2 against an fp32 run of the reference arithmetic on the same (bf16-rounded)
+inputs.  Integer / byte work (layout maps, cache writes without rotation) must be bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import monarch_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+REL_L2 = 1e-2
+
+
+@pytest.fixture(scope="module")
+def sfb():
+    import self_forcing_b200
+    assert torch.cuda.is_available()
+    return self_forcing_b200
+
+
+def bf(x):
+    return x.to(torch.bfloat16)
+
+
+def check_close(got, ref, what=""):
+    got = got.float().cpu()
+    ref = ref.float().cpu()
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    assert torch.isfinite(got).all(), f"{what}: non-finite output"
+    err = (got - ref).abs().max().item()
+    rel = ((got - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+    assert err <= MAX_ABS and rel <= REL_L2, f"{what}: max-abs {err:.3e} rel-L2 {rel:.3e}"
+    return err, rel
+
+
+def small_case(ci, iters, D=128, seed=None, B=2, H=2, chunks_cached=3):
+    """Like cases.cache_case but at head_dim 128 (the only size the kernels are built for)."""
+    name, ft, hr, wr, h, w = cases.SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(5000 + 10 * ci + iters if seed is None else seed)
+    chunk = 3 * h * w
+    n_buf, n_kv = (chunks_cached + 1) * chunk, chunks_cached * chunk
+    mk = lambda *s: bf(cases.randn(rng, *s))
+    return dict(name=name, blocking=(ft, hr, wr, h, w), q=mk(B, chunk, H, D), nk=mk(B, chunk, H, D),
+                nv=mk(B, chunk, H, D), kbuf=mk(B, n_buf, H, D), vbuf=mk(B, n_buf, H, D),
+                start=n_kv - chunk, end=n_kv, n_kv=n_kv, sm_scale=D ** -0.5)
+
+
+def run_oracle_cache(c, iters=1):
+    kc, vc = c["kbuf"].float().clone(), c["vbuf"].float().clone()
+    n_kv = c["n_kv"]
+    z = orc.monarch_attn_with_kv_cache(c["q"].float(), kc[:, :n_kv], vc[:, :n_kv], c["nk"].float(), c["nv"].float(),
+                                       c["start"], c["end"], *c["blocking"], sm_scale=c["sm_scale"], num_iters=iters)
+    return z, kc, vc
+
+
+def run_gpu_cache(sfb, c, iters=1):
+    dev = "cuda"
+    kc, vc = c["kbuf"].to(dev).clone(), c["vbuf"].to(dev).clone()
+    n_kv = c["n_kv"]
+    z = sfb.monarch_attn_with_kv_cache(c["q"].to(dev), kc[:, :n_kv], vc[:, :n_kv], c["nk"].to(dev), c["nv"].to(dev),
+                                       c["start"], c["end"], *c["blocking"], sm_scale=c["sm_scale"], num_iters=iters)
+    torch.cuda.synchronize()
+    return z, kc, vc
+
+
+# ------------------------------------------------------------------------------- layout / rope
+@pytest.mark.parametrize("ci", range(len(cases.SMALL_BLOCKINGS)))
+def test_cache_write_bit_exact(sfb, ci):
+    c = small_case(ci, 1)
+    z_ref, kc_ref, vc_ref = run_oracle_cache(c)
+    z, kc, vc = run_gpu_cache(sfb, c)
+    assert torch.equal(kc.cpu().float(), kc_ref), "K cache after the in-place write differs"
+    assert torch.equal(vc.cpu().float(), vc_ref), "V cache after the in-place write differs"
+
+
+def test_cache_write_real_grid_bit_exact(sfb):
+    """Permuted blocking on the real 30x52 grid, 12 heads: the written slot equals the oracle's map."""
+    rng = np.random.default_rng(77)
+    B, H, D, h, w = 1, 12, 128, 30, 52
+    n = 3 * h * w
+    nk, nv = bf(cases.randn(rng, B, n, H, D)), bf(cases.randn(rng, B, n, H, D))
+    q = bf(cases.randn(rng, B, n, H, D))
+    kc = torch.zeros(B, 2 * n, H, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    sfb.monarch_attn_with_kv_cache(q.cuda(), kc, vc, nk.cuda(), nv.cuda(), n, 2 * n, 1, 2, 4, h, w)
+    _, mon2nat = orc.token_maps(n, 1, 2, 4, h, w)
+    assert torch.equal(kc[:, n:].cpu(), nk[:, torch.from_numpy(mon2nat)])
+    assert torch.equal(vc[:, n:].cpu(), nv[:, torch.from_numpy(mon2nat)])
+    assert not kc[:, :n].any() and not vc[:, :n].any()
+
+
+def ulp_mismatch(a, b):
+    """Count of elements differing, and max difference in bf16 ulps (via the int16 bit patterns)."""
+    ai = a.contiguous().view(torch.int16).to(torch.int32)
+    bi = b.contiguous().view(torch.int16).to(torch.int32)
+    # sign-magnitude -> monotonic integer
+    ai = torch.where(ai < 0, -(ai & 0x7FFF), ai)
+    bi = torch.where(bi < 0, -(bi & 0x7FFF), bi)
+    d = (ai - bi).abs()
+    return int((d > 0).sum()), int(d.max())
+
+
+@pytest.mark.parametrize("sf", [0, 9])
+def test_rope_standalone(sfb, golden, sf):
+    x, grid = cases.rope_inputs()
+    xb = bf(x)
+    ref = orc.rope_apply(xb, grid, start_frame=sf)            # fp64 rotation, one rounding to bf16
+    if sf == 9:
+        assert np.array_equal(ref.float().numpy(), golden["rope_out_bf16_sf9"])
+    grid_t = torch.tensor([list(grid)] * x.shape[0])
+    got = sfb.causal_rope_apply(xb.cuda(), grid_t, None, start_frame=sf).cpu()
+    n_diff, max_ulp = ulp_mismatch(got, ref)
+    # fp32 rotation vs fp64: only rounding ties may move, by one ulp
+    assert max_ulp <= 1 and n_diff <= 0.002 * got.numel(), (n_diff, max_ulp)
+    # pass-through tail is exact
+    assert torch.equal(got[:, 105:], xb[:, 105:])
+
+
+def test_rope_fused_front_end(sfb):
+    """RoPE + layout + cache write in one kernel == separate rotation followed by the plain op."""
+    rng = np.random.default_rng(11)
+    B, H, D, h, w = 2, 3, 128, 6, 8
+    n = 3 * h * w
+    q, k, v = (bf(cases.randn(rng, B, n, H, D)).cuda() for _ in range(3))
+    kbuf = bf(cases.randn(rng, B, 3 * n, H, D)).cuda()
+    vbuf = bf(cases.randn(rng, B, 3 * n, H, D)).cuda()
+    grid_t = torch.tensor([[3, h, w]] * B)
+    for ft, hr, wr in ((1, 1, 1), (1, 2, 4), (3, 1, 1)):
+        k1, v1, k2, v2 = kbuf.clone(), vbuf.clone(), kbuf.clone(), vbuf.clone()
+        z1 = sfb.rope_monarch_attn_with_kv_cache(q, k, v, k1[:, :2 * n], v1[:, :2 * n], n, 2 * n, 3, ft, hr, wr, h, w)
+        rq = sfb.causal_rope_apply(q, grid_t, None, start_frame=3)
+        rk = sfb.causal_rope_apply(k, grid_t, None, start_frame=3)
+        z2 = sfb.monarch_attn_with_kv_cache(rq, k2[:, :2 * n], v2[:, :2 * n], rk, v, n, 2 * n, ft, hr, wr, h, w)
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)
+        assert torch.equal(z1, z2)
+        # and against the oracle's fp64 rotation
+        ref_k = orc.rope_apply(k.cpu(), (3, h, w), start_frame=3)
+        _, mon2nat = orc.token_maps(n, ft, hr, wr, h, w)
+        n_diff, max_ulp = ulp_mismatch(k1[:, n:2 * n].cpu(), ref_k[:, torch.from_numpy(mon2nat)])
+        assert max_ulp <= 1 and n_diff <= 0.002 * ref_k.numel()
+
+
+# ------------------------------------------------------------------------------- Monarch, T = 1
+@pytest.mark.parametrize("ci", range(len(cases.SMALL_BLOCKINGS)))
+def test_monarch_small_blockings(sfb, ci):
+    c = small_case(ci, 1)
+    z_ref, _, _ = run_oracle_cache(c)
+    z, _, _ = run_gpu_cache(sfb, c)
+    check_close(z, z_ref, c["name"])
+
+
+@pytest.mark.parametrize("blk", cases.REAL_BLOCKINGS)
+def test_monarch_real_block_sizes_vs_golden(sfb, golden, blk):
+    """30x52 grid, D=128, one head: compare with the fixture computed by the reference's own code
+    (fp32 inputs there; the GPU sees them rounded to bf16, which the tolerance covers)."""
+    name, ft, hr, wr = blk
+    c = cases.real_case()
+    kc, vc = bf(c["kbuf"]).cuda(), bf(c["vbuf"]).cuda()
+    z = sfb.monarch_attn_with_kv_cache(bf(c["q"]).cuda(), kc, vc, bf(c["nk"]).cuda(), bf(c["nv"]).cuda(),
+                                       c["start"], c["end"], ft, hr, wr, c["h"], c["w"])
+    ref = torch.from_numpy(golden[f"real_{name}_z_sample"])
+    check_close(z[0, ::37, 0, :], ref, name)
+
+
+def test_monarch_baseline_config1_vs_golden(sfb, golden):
+    c = cases.c1_case()
+    kc = torch.zeros(1, c["chunk"], 12, 128, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    z = sfb.monarch_attn_with_kv_cache(bf(c["q"]).cuda(), kc, vc, bf(c["k"]).cuda(), bf(c["v"]).cuda(), 0, c["chunk"],
+                                       1, 1, 1, c["h"], c["w"])
+    check_close(z[0, ::97, ::5, :], torch.from_numpy(golden["c1_T1_z_sample"]), "config 1, T=1")
+
+
+@pytest.mark.parametrize("name,ft,hr,wr,k_chunks", [("framewise", 1, 1, 1, 7), ("tied3frame", 3, 1, 1, 4),
+                                                      ("reduce2xh", 1, 2, 1, 3), ("reduce4xw2xh", 1, 2, 4, 2)])
+def test_monarch_rollout_shapes_vs_oracle(sfb, name, ft, hr, wr, k_chunks):
+    """Wan-1.3B chunk (4680 queries) against k cached chunks; 2 of the heads are checked on the CPU."""
+    rng = np.random.default_rng(900 + k_chunks)
+    B, H, D, h, w = 1, 4, 128, 30, 52
+    n = 3 * h * w
+    n_kv = k_chunks * n
+    mk = lambda *s: bf(cases.randn(rng, *s))
+    q, nk, nv = mk(B, n, H, D), mk(B, n, H, D), mk(B, n, H, D)
+    kbuf, vbuf = mk(B, 7 * n, H, D), mk(B, 7 * n, H, D)
+    kc, vc = kbuf.cuda().clone(), vbuf.cuda().clone()
+    z = sfb.monarch_attn_with_kv_cache(q.cuda(), kc[:, :n_kv], vc[:, :n_kv], nk.cuda(), nv.cuda(), n_kv - n, n_kv,
+                                       ft, hr, wr, h, w)
+    hs = [0, 3]
+    kr, vr = kbuf[:, :, hs].float().clone(), vbuf[:, :, hs].float().clone()
+    z_ref = orc.monarch_attn_with_kv_cache(q[:, :, hs].float(), kr[:, :n_kv], vr[:, :n_kv], nk[:, :, hs].float(),
+                                           nv[:, :, hs].float(), n_kv - n, n_kv, ft, hr, wr, h, w)
+    check_close(z[:, :, hs], z_ref, f"{name} k={k_chunks}")
+
+
+def test_monarch_chunking_is_invisible(sfb, monkeypatch):
+    """The bridge budget only changes how the work is cut into launches, never the result."""
+    c = small_case(3, 1, B=2, H=3)
+    z_a, _, _ = run_gpu_cache(sfb, c)
+    monkeypatch.setenv("SFM_BRIDGE_MB", "1")
+    z_b, _, _ = run_gpu_cache(sfb, c)
+    assert torch.equal(z_a, z_b)
+
+
+def test_monarch_properties_full_size(sfb):
+    """Size-independent properties at the full benchmark size (12 heads, 32760 cached tokens):
+    (1) bitwise run-to-run determinism, (2) a constant V comes back unchanged (all softmax
+    weights sum to one), (3) heads are independent (a 1-head call equals that head of the
+    12-head call)."""
+    rng = np.random.default_rng(4242)
+    B, H, D, h, w = 1, 12, 128, 30, 52
+    n, n_kv = 3 * h * w, 7 * 3 * h * w
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn(B, n, H, D, device="cuda", generator=g).bfloat16()
+    kc = torch.randn(B, n_kv, H, D, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(B, n_kv, H, D, device="cuda", generator=g).bfloat16()
+    nk, nv = kc[:, -n:].clone(), vc[:, -n:].clone()
+    z1 = sfb.monarch_attn_with_kv_cache(q, kc, vc, nk, nv, n_kv - n, n_kv, 1, 1, 1, h, w)
+    z2 = sfb.monarch_attn_with_kv_cache(q, kc, vc, nk, nv, n_kv - n, n_kv, 1, 1, 1, h, w)
+    assert torch.equal(z1, z2)
+    const = torch.linspace(-2, 2, D, device="cuda").bfloat16().expand(B, n_kv, H, D).contiguous()
+    zc = sfb.monarch_attn_with_kv_cache(q, kc, const.clone(), nk, const[:, -n:].clone(), n_kv - n, n_kv, 1, 1, 1, h, w)
+    assert (zc.float() - const[:, :n].float()).abs().max().item() <= 2e-2
+    hsel = 5
+    k1, v1 = kc[:, :, hsel:hsel + 1].contiguous(), vc[:, :, hsel:hsel + 1].contiguous()
+    zh = sfb.monarch_attn_with_kv_cache(q[:, :, hsel:hsel + 1].contiguous(), k1, v1, k1[:, -n:].clone(),
+                                        v1[:, -n:].clone(), n_kv - n, n_kv, 1, 1, 1, h, w)
+    assert torch.equal(zh[:, :, 0], z1[:, :, hsel])
+
+
+# ------------------------------------------------------------------------------- Monarch, T > 1
+@pytest.mark.parametrize("ci", range(len(cases.SMALL_BLOCKINGS)))
+@pytest.mark.parametrize("iters", [2, 5])
+def test_monarch_iterative_small(sfb, ci, iters):
+    c = small_case(ci, iters)
+    z_ref, _, _ = run_oracle_cache(c, iters)
+    z, _, _ = run_gpu_cache(sfb, c, iters)
+    check_close(z, z_ref, f"{c['name']} T={iters}")
+
+
+def test_monarch_baseline_config1_T20_vs_golden(sfb, golden):
+    c = cases.c1_case()
+    kc = torch.zeros(1, c["chunk"], 12, 128, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    z = sfb.monarch_attn_with_kv_cache(bf(c["q"]).cuda(), kc, vc, bf(c["k"]).cuda(), bf(c["v"]).cuda(), 0, c["chunk"],
+                                       1, 1, 1, c["h"], c["w"], num_iters=20)
+    check_close(z[0, ::97, ::5, :], torch.from_numpy(golden["c1_T20_z_sample"]), "config 1, T=20")
+
+
+# ------------------------------------------------------------------------------- no-cache entry point
+@pytest.mark.parametrize("ci", range(4))
+def test_monarch_nocache_and_block_causal(sfb, ci):
+    name, ft, hr, wr, h, w = cases.SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(6000 + ci)
+    B, H, D = 2, 2, 128
+    n = 6 * h * w
+    q, k, v = (bf(cases.randn(rng, B, n, H, D)) for _ in range(3))
+    for iters in (1, 3):
+        ref = orc.monarch_attn(q.float(), k.float(), v.float(), ft, hr, wr, h, w, num_iters=iters)
+        got = sfb.monarch_attn(q.cuda(), k.cuda(), v.cuda(), ft, hr, wr, h, w, num_iters=iters)
+        check_close(got, ref, f"{name} no-cache T={iters}")
+    bc = 3 * h * w
+    ref = orc.monarch_attn(q.float(), k.float(), v.float(), ft, hr, wr, h, w, block_causal_size=bc)
+    got = sfb.monarch_attn(q.cuda(), k.cuda(), v.cuda(), ft, hr, wr, h, w, block_causal_size=bc)
+    check_close(got, ref, f"{name} block-causal")
+
+
+# ------------------------------------------------------------------------------- dense path
+@pytest.mark.parametrize("n_q,n_kv", [(50, 170), (4680, 4680), (333, 1000)])
+def test_dense_attention(sfb, n_q, n_kv):
+    rng = np.random.default_rng(31 + n_q)
+    B, H, D = 2, 3, 128
+    q, k, v = bf(cases.randn(rng, B, n_q, H, D)), bf(cases.randn(rng, B, n_kv + 64, H, D)), bf(cases.randn(rng, B, n_kv + 64, H, D))
+    kd, vd = k.cuda(), v.cuda()
+    got = sfb.attention(q.cuda(), kd[:, :n_kv], vd[:, :n_kv])      # strided views, as the model passes them
+    ref = orc.dense_attention(q.float(), k[:, :n_kv].float(), v[:, :n_kv].float())
+    check_close(got, ref, f"dense {n_q}x{n_kv}")
+
+
+def test_dense_with_cache_write(sfb):
+    rng = np.random.default_rng(8)
+    B, H, D, n = 1, 2, 128, 96
+    q, nk, nv = (bf(cases.randn(rng, B, n, H, D)) for _ in range(3))
+    kbuf, vbuf = bf(cases.randn(rng, B, 3 * n, H, D)), bf(cases.randn(rng, B, 3 * n, H, D))
+    kc, vc = kbuf.cuda().clone(), vbuf.cuda().clone()
+    got = sfb.full_attention_with_kv_cache(q.cuda(), kc[:, :2 * n], vc[:, :2 * n], nk.cuda(), nv.cuda(), n, 2 * n)
+    kr, vr = kbuf.clone(), vbuf.clone()
+    kr[:, n:2 * n] = nk
+    vr[:, n:2 * n] = nv
+    assert torch.equal(kc.cpu(), kr) and torch.equal(vc.cpu(), vr)
+    ref = orc.dense_attention(q.float(), kr[:, :2 * n].float(), vr[:, :2 * n].float())
+    check_close(got, ref, "dense after cache write")
+
+
+def test_errors_are_loud(sfb):
+    q = torch.zeros(1, 1560, 1, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):            # cache extent not a whole number of groups
+        sfb.monarch_attn_with_kv_cache(q, torch.zeros(1, 1600, 1, 128, dtype=torch.bfloat16, device="cuda"),
+                                       torch.zeros(1, 1600, 1, 128, dtype=torch.bfloat16, device="cuda"),
+                                       q, q, 40, 1600, 1, 1, 1, 30, 52)
+    with pytest.raises(TypeError):
+        sfb.attention(q.float().half(), q.half(), q.half(), dtype=torch.float16)
+    with pytest.raises(ValueError):
+        sfb.attention(torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device="cuda"),
+                      torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device="cuda"),
+                      torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device="cuda"))
