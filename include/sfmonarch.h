@@ -128,6 +128,15 @@ int sfm_monarch_fwd(const void* q, int64_t q_batch_stride,
                     float sm_scale, int num_iters, size_t bridge_budget_bytes, void* stream);
 
 /*
+ * Waits for the work queued on `stream` and reports whether any kernel of the last
+ * sfm_monarch_fwd call that used `workspace` gave up on an internal wait (every device-side
+ * wait is bounded): SFM_OK or SFM_ERR_DEVICE_STATUS.  Synchronises the stream; meant for
+ * tests and debugging.
+ * Replaces: nothing in the reference (its Triton kernels have no device-side status).
+ */
+int sfm_workspace_status(const void* workspace, void* stream);
+
+/*
  * Block-causal Monarch attention without a cache: q, k, v [B, N, H, D] natural order,
  * contiguous.  Query groups of causal block c attend the key groups of blocks 0..c;
  * causal_groups = groups per causal block (0 = no mask).  k_mon / v_mon are scratch

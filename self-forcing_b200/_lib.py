@@ -27,6 +27,7 @@ SIGNATURES = {
                                 [C.c_float, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "sfm_dense_fwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p] +
                       [C.c_int] * 5 + [C.c_float, C.c_void_p]),
+    "sfm_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sfm_launch_count": (C.c_longlong, []),
     "sfm_profile_enable": (C.c_int, [C.c_int]),
     "sfm_profile_read": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),

@@ -3,8 +3,14 @@
 #include <cstdlib>
 
 #include "monarch_params.cuh"
+#include "tc05.cuh"
 
 using namespace sfm;
+
+namespace sfm {
+int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps, int rows_per_group, int n_s, int* status,
+                     cudaStream_t s);
+}
 
 namespace {
 
@@ -17,7 +23,7 @@ struct Plan {
     Blocking blk;
     int A, F, n_keys;
     int nbh_chunk, na_chunk, na_cta;
-    size_t off_aL, off_Y, off_cL, off_lse, off_aR, off_cR, total;
+    size_t off_status, off_aL, off_Y, off_cL, off_lse, off_aR, off_cR, total;
 };
 
 int make_plan(Plan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce, int h,
@@ -56,6 +62,7 @@ int make_plan(Plan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int 
     }
     const size_t aj = (size_t)pl->nbh_chunk * pl->na_chunk * blk.b2;
     size_t off = 0;
+    pl->off_status = off; off = align256(off + sizeof(int));
     pl->off_aL = off; off = align256(off + aj * pl->n_keys * kHeadDim * 2);
     pl->off_Y = off;  off = align256(off + aj * pl->n_keys * kHeadDim * 2);
     pl->off_cL = off; off = align256(off + aj * pl->n_keys * 4);
@@ -99,13 +106,42 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     p.scale = sm_scale;
     p.blk = pl.blk;
 
+    // Tensor-core path: single pass, no causal mask.  The iterative and block-causal variants run
+    // on the mma.sync kernels.
+    const bool use_tc = (num_iters == 1 && causal_groups == 0);
+    int* status = reinterpret_cast<int*>(base + pl.off_status);
+    CUtensorMap maps[5];
+    const int rows_per_group = (pl.blk.b2 + 7) & ~7;
+    const int n_s = (pl.blk.b2 + 15) & ~15;
+    if (use_tc) {
+        cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
+        const uint64_t row = (uint64_t)kHeadDim * 2, tok = (uint64_t)H * row;
+        uint64_t dq[4] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)n_q, (uint64_t)B};
+        uint64_t sq[3] = {row, tok, (uint64_t)q_bs * 2};
+        uint32_t bq[4] = {64, 1, (uint32_t)rows_per_group, 1};
+        uint64_t dk[4] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)n_kv, (uint64_t)B};
+        uint64_t sk[3] = {row, tok, (uint64_t)c_bs * 2};
+        uint32_t bk[4] = {64, 1, (uint32_t)n_s, 1};
+        const uint64_t n_aj = (uint64_t)pl.nbh_chunk * pl.na_chunk * pl.blk.b2;
+        uint64_t db[3] = {(uint64_t)kHeadDim, (uint64_t)pl.n_keys, n_aj};
+        uint64_t sb[2] = {row, (uint64_t)pl.n_keys * row};
+        uint32_t bb[3] = {64, 1, (uint32_t)pl.blk.b2};
+        if ((rc = make_tmap_bf16(&maps[0], q, 4, dq, sq, bq))) return rc;
+        if ((rc = make_tmap_bf16(&maps[1], kc, 4, dk, sk, bk))) return rc;
+        if ((rc = make_tmap_bf16(&maps[2], vc, 4, dk, sk, bk))) return rc;
+        if ((rc = make_tmap_bf16(&maps[3], p.aL, 3, db, sb, bb))) return rc;
+        if ((rc = make_tmap_bf16(&maps[4], p.Y, 3, db, sb, bb))) return rc;
+    }
+
     const int BH = B * H;
     for (int bh0 = 0; bh0 < BH; bh0 += pl.nbh_chunk) {
         p.bh0 = bh0; p.nbh = std::min(pl.nbh_chunk, BH - bh0);
         for (int a0 = 0; a0 < pl.A; a0 += pl.na_chunk) {
             p.a0 = a0; p.na = std::min(pl.na_chunk, pl.A - a0);
             // enough row-step CTAs to fill the GPU about twice over
-            int asubs = (p.na + p.na_cta - 1) / p.na_cta;
+            int asubs = use_tc ? (p.na + (128 / rows_per_group) - 1) / (128 / rows_per_group)
+                               : (p.na + p.na_cta - 1) / p.na_cta;
             int base_ctas = pl.blk.b1 * asubs * p.nbh;
             int fsplit = std::max(1, std::min(pl.F, (2 * 148 + base_ctas - 1) / base_ctas));
             p.f_per = (pl.F + fsplit - 1) / fsplit;
@@ -116,7 +152,11 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                 p.use_aR = it > 0;
                 p.write_Y = last;
                 p.mult0 = num_iters > 1 ? sm_scale * (1.0f / (1.0f + 1e-6f)) : sm_scale;
-                if ((rc = launch_r_step(p, stream))) return rc;
+                if (use_tc) {
+                    if ((rc = launch_r_step_tc(p, maps, rows_per_group, n_s, status, stream))) return rc;
+                } else {
+                    if ((rc = launch_r_step(p, stream))) return rc;
+                }
                 if (last) {
                     if ((rc = launch_l_step(p, 0, stream))) return rc;
                 } else {
@@ -132,6 +172,16 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
 }  // namespace
 
 extern "C" int sfm_version(void) { return 100; }
+
+// Reads (and thereby waits for) the status word the kernels of the last call on `workspace` left.
+extern "C" int sfm_workspace_status(const void* workspace, void* stream) {
+    if (!workspace) return SFM_ERR_NULL_POINTER;
+    int st = 0;
+    cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    return st == 0 ? SFM_OK : SFM_ERR_DEVICE_STATUS;
+}
 
 extern "C" const char* sfm_error_string(int code) {
     switch (code) {

@@ -8,6 +8,7 @@ is reused by later calls on the same stream order (the reference is single-strea
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Optional, Tuple
 
 import numpy as np
@@ -118,6 +119,8 @@ def _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale
                              _ptr(out), _ptr(ws), ws.numel(), B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w,
                              float(sm_scale), int(num_iters), 0, _stream())
     _lib.check(rc, "sfm_monarch_fwd")
+    if os.environ.get("SFM_CHECK_STATUS") == "1":      # debugging aid: synchronises the stream
+        _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
     return out
 
 

@@ -4,6 +4,7 @@ from pathlib import Path
 
 import pytest
 
+os.environ.setdefault("SFM_CHECK_STATUS", "1")   # tests read the kernels' status word after every call
 ROOT = Path(__file__).resolve().parent.parent
 for p in (ROOT, ROOT / "tests" / "golden"):
     if str(p) not in sys.path:
