@@ -9,7 +9,7 @@ using namespace sfm;
 
 namespace sfm {
 int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps, int rows_per_group, int n_s, int* status,
-                     cudaStream_t s);
+                     int num_sms, cudaStream_t s);
 }
 
 namespace {
@@ -109,6 +109,11 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     // Tensor-core path: single pass, no causal mask.  The iterative and block-causal variants run
     // on the mma.sync kernels.
     const bool use_tc = (num_iters == 1 && causal_groups == 0);
+    int num_sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
     int* status = reinterpret_cast<int*>(base + pl.off_status);
     CUtensorMap maps[5];
     const int rows_per_group = (pl.blk.b2 + 7) & ~7;
@@ -143,7 +148,12 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
             int asubs = use_tc ? (p.na + (128 / rows_per_group) - 1) / (128 / rows_per_group)
                                : (p.na + p.na_cta - 1) / p.na_cta;
             int base_ctas = pl.blk.b1 * asubs * p.nbh;
-            int fsplit = std::max(1, std::min(pl.F, (2 * 148 + base_ctas - 1) / base_ctas));
+            int fsplit;
+            if (use_tc) {   // persistent CTAs: about three units per SM, at least four steps per unit
+                fsplit = std::max(1, std::min(std::max(1, pl.F / 4), (3 * num_sms + base_ctas - 1) / base_ctas));
+            } else {
+                fsplit = std::max(1, std::min(pl.F, (2 * num_sms + base_ctas - 1) / base_ctas));
+            }
             p.f_per = (pl.F + fsplit - 1) / fsplit;
             p.fsplit = (pl.F + p.f_per - 1) / p.f_per;
 
@@ -153,7 +163,7 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                 p.write_Y = last;
                 p.mult0 = num_iters > 1 ? sm_scale * (1.0f / (1.0f + 1e-6f)) : sm_scale;
                 if (use_tc) {
-                    if ((rc = launch_r_step_tc(p, maps, rows_per_group, n_s, status, stream))) return rc;
+                    if ((rc = launch_r_step_tc(p, maps, rows_per_group, n_s, status, num_sms, stream))) return rc;
                 } else {
                     if ((rc = launch_r_step(p, stream))) return rc;
                 }

@@ -87,6 +87,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Same packing without the conversion instruction (which issues on the 16-lane transcendental
+// pipe, shared with exp2): add half an ulp of bf16 to the fp32 bit patterns and keep the upper
+// halves.  Rounds to nearest with ties away from zero in magnitude; Inf stays Inf.
+__device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));

@@ -1,19 +1,28 @@
 // Monarch row step on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// One CTA owns (batch*head, block row k, a range of cached groups f, one tile of stacked query
-// groups).  A tile stacks up to 128 query rows r = (query group a, column j); each group is padded to
-// a multiple of 8 rows so that its 128-byte-swizzled shared-memory image starts on a swizzle atom.
-// For every f the CTA computes, per query row, a complete softmax over the b2 keys of K[f,k,:]:
+// Work is cut into units (batch*head, tile of stacked query groups, block row k, range of cached
+// groups f).  A tile stacks up to 128 query rows r = (query group a, column j); each group is padded
+// to a multiple of 8 rows so that its 128-byte-swizzled shared-memory image starts on a swizzle atom.
+// CTAs are persistent: each walks the unit list with a fixed stride and, for every (unit, f),
+// computes per query row a complete softmax over the b2 keys of K[f,k,:]:
 //   S  = Q_tile K[f,k]^T                 tcgen05.mma, both operands from shared memory (K-major)
 //   P  = softmax rows of S (scaled)      one thread per row: tcgen05.ld, registers, tcgen05.st (bf16)
-//   aL = P K[f,k],  Y = P V[f,k]         tcgen05.mma, A = P from TMEM, B = the same K / V tile (MN-major)
+//   [aL | Y] = P [K[f,k] | V[f,k]]       one N=256 tcgen05.mma per 16 keys, A = P from TMEM,
+//                                        B = the K and V tiles side by side (MN-major)
 //   cL = sum_l P ln P                    from the softmax registers
 // and streams aL, Y (bf16) to the chunk's bridge with TMA stores; cL goes out with plain stores.
 //
-// Warp roles (10 warps): 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
-// 2..5 = softmax warpgroup, 6..9 = epilogue warpgroup.  S/P is double buffered in TMEM so the
-// S GEMM of step i+1 overlaps the softmax of step i; the two output accumulators are single
-// buffered.  Every wait is bounded; on a timeout the CTA records a status code and unwinds.
+// Warp roles (20 warps): 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
+// 2..3 = TMA store issuers for the aL / Y halves of the accumulator,
+// 4..7 and 8..11 = two softmax warpgroups that take even / odd steps (each owns one of the two
+// S/P buffers in TMEM), 12..15 and 16..19 = two epilogue warpgroups (aL half / Y half of the
+// accumulator).  The S GEMM of step i+1 overlaps the softmax of step i; the output accumulator is
+// single buffered and handed back to the MMA warp as soon as both halves sit in registers.  Each
+// epilogue warpgroup converts its 128 columns in two 64-column halves into a two-slot staging ring
+// that its store-issuing warp drains with TMA, so conversion and stores overlap.  All roles run the same unit loop and meet
+// only through mbarriers whose phases follow running step counters, so the pipeline keeps flowing
+// across unit boundaries.  Every wait is bounded; on a timeout the CTA records a status code and
+// unwinds.
 //
 // Arithmetic follows monarch_attn_ref_op (wan/modules/monarch_attn.py:1813-1823, 1828); the sqrt(s)
 // scaling of q and k is folded into the softmax scale, so aL here is the reference's aL / sqrt(s).
@@ -28,42 +37,75 @@ using namespace tc;
 namespace {
 
 constexpr int kStages = 3;            // K/V tile ring
-constexpr int kThreads = 320;
+constexpr int kThreads = 640;
 constexpr int kTileRows = 128;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColOK = 128, kColOV = 256;
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128;   // O = [aL | Y], 256 columns
 
 struct RTcParams {
     MonarchParams mp;
     int rows_per_group;    // b2 padded to a multiple of 8
     int groups_per_tile;   // 128 / rows_per_group
-    int n_s;               // b2 padded to a multiple of 16: key rows per K/V tile and N of the S GEMM
+    int tiles;             // tiles per (batch*head) of the chunk
+    int n_units;           // nbh * tiles * b1 * fsplit
     int* status;           // device status word (0 = ok)
+#ifdef SFM_TRACE
+    long long* trace;      // debug build only: per-role, per-step cycle stamps of CTA 0
+#endif
 };
 
+#ifdef SFM_TRACE
+#define TRACE(role, it, ev) do { if ((it) < 32) trace_s[((role) * 32 + (it)) * 4 + (ev)] = clock64(); } while (0)
+#else
+#define TRACE(role, it, ev) do {} while (0)
+#endif
+
+struct RUnit {
+    int bhl, tile, k, f_begin, n_it;
+};
+
+__device__ __forceinline__ RUnit decode_unit(const RTcParams& rp, int u) {
+    const MonarchParams& p = rp.mp;
+    RUnit r;
+    int fs = u % p.fsplit; u /= p.fsplit;
+    r.k = u % p.blk.b1; u /= p.blk.b1;
+    r.tile = u % rp.tiles;
+    r.bhl = u / rp.tiles;
+    r.f_begin = fs * p.f_per;
+    r.n_it = min(p.F, r.f_begin + p.f_per) - r.f_begin;
+    return r;
+}
+
 struct __align__(8) Barriers {
-    uint64_t q_full;
+    uint64_t q_full, q_empty;
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
     uint64_t s_full[2];
     uint64_t p_full[2];
     uint64_t o_full;
     uint64_t o_free;
+    uint64_t stg_full[2][2];   // [tensor][slot]: 128 epilogue threads have filled the slot
+    uint64_t stg_free[2][2];   // [tensor][slot]: the TMA store has finished reading the slot
     uint32_t tmem_base;
     volatile int abort_flag;
 };
 
 // shared memory carve-up (bytes from a 1024-aligned base)
 constexpr int kQBytes = 2 * kTileRows * 128;               // two 64-column halves
-constexpr int kKVTileBytes = 2 * 64 * 128;                 // one K or V tile (up to 64 rows), two halves
-constexpr int kStageBytes = 2 * kKVTileBytes;              // K + V
+constexpr int kStageBytes = 4 * 64 * 128;                  // K half 0, K half 1, V half 0, V half 1 (<= 64 rows each)
 constexpr int kStagingBytes = 2 * kQBytes;                 // aL and Y, bf16, TMA-store source
 constexpr int kSmemBytes = 1024 + kQBytes + kStages * kStageBytes + kStagingBytes + 256;
+
+// Register budget per warpgroup (the kernel launches with 640 threads at 96 registers each): the
+// control warpgroup gives registers back, the compute warpgroups take more.
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
+template <int N_S>
 __global__ void __launch_bounds__(kThreads, 1)
 monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tal,
@@ -75,26 +117,27 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     unsigned char* stg_s = kv_s + kStages * kStageBytes;
     Barriers* bars = reinterpret_cast<Barriers*>(stg_s + kStagingBytes);
 
+#ifdef SFM_TRACE
+    __shared__ long long trace_s[8 * 32 * 4];
+    for (int i = threadIdx.x; i < 8 * 32 * 4; i += blockDim.x) trace_s[i] = 0;
+    __syncthreads();
+#endif
     const MonarchParams& p = rp.mp;
     const Blocking& blk = p.blk;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b1 = blk.b1, b2 = blk.b2;
-    const int k = blockIdx.x % b1, fs = blockIdx.x / b1;
-    const int g_first = blockIdx.y * rp.groups_per_tile;                 // chunk-local first group of the tile
-    const int ng = min(rp.groups_per_tile, p.na - g_first);
-    const int bhl = blockIdx.z, bh = p.bh0 + bhl, b = bh / p.H, hd = bh - b * p.H;
-    const int f_begin = fs * p.f_per, f_end = min(p.F, f_begin + p.f_per);
-    const int n_it = f_end - f_begin;
     const int RG = rp.rows_per_group;
-    const int n_s = rp.n_s;
-    const int valid_rows = ng * RG;                                       // rows of the tile that carry groups
+    constexpr int kHalf = N_S * 128;                    // bytes of one 64-column half of a K or V tile
 
     if (tid == 0) {
         mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->q_empty, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->s_full[s], 1); mbar_init(&bars->p_full[s], 128); }
         mbar_init(&bars->o_full, 1);
-        mbar_init(&bars->o_free, 128);
+        mbar_init(&bars->o_free, 256);
+        for (int e = 0; e < 2; ++e)
+            for (int h = 0; h < 2; ++h) { mbar_init(&bars->stg_full[e][h], 128); mbar_init(&bars->stg_free[e][h], 1); }
         bars->abort_flag = 0;
         mbar_init_fence();
     }
@@ -103,232 +146,333 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
-    if (n_it <= 0) {   // uniform for the CTA
-        __syncthreads();
-        if (warp == 1) tmem_dealloc(tmem, kTmemCols);
-        return;
-    }
 
     auto fail = [&](int code) {
         bars->abort_flag = 1;
         atomicCAS(rp.status, 0, code);
     };
+    const int u_first = blockIdx.x, u_stride = gridDim.x;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv);
-            mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ng * RG * 256));
-            for (int g = 0; g < ng; ++g) {
-                int tok = blk.row_token(p.a0 + g_first + g, k);
-                tma_load_4d(q_s + g * RG * 128, &tq, &bars->q_full, 0, hd, tok, b);
-                tma_load_4d(q_s + kTileRows * 128 + g * RG * 128, &tq, &bars->q_full, 64, hd, tok, b);
-            }
-            for (int i = 0; i < n_it && !bars->abort_flag; ++i) {
-                const int s = i % kStages;
-                if (i >= kStages && !mbar_wait(&bars->kv_empty[s], ((i / kStages) - 1) & 1)) { fail(11); break; }
-                const int tok = ((f_begin + i) * b1 + k) * b2;
-                unsigned char* ks = kv_s + s * kStageBytes;
-                unsigned char* vs = ks + kKVTileBytes;
-                mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(4 * n_s * 128));
-                tma_load_4d(ks, &tk, &bars->kv_full[s], 0, hd, tok, b);
-                tma_load_4d(ks + n_s * 128, &tk, &bars->kv_full[s], 64, hd, tok, b);
-                tma_load_4d(vs, &tv, &bars->kv_full[s], 0, hd, tok, b);
-                tma_load_4d(vs + n_s * 128, &tv, &bars->kv_full[s], 64, hd, tok, b);
+            int g = 0, uc = 0;
+            for (int u = u_first; u < rp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+                const RUnit un = decode_unit(rp, u);
+                const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
+                const int g_first = un.tile * rp.groups_per_tile;
+                const int ng = min(rp.groups_per_tile, p.na - g_first);
+                if (uc > 0 && !mbar_wait(&bars->q_empty, (uc - 1) & 1)) { fail(10); break; }
+                mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ng * RG * 256));
+                for (int gi = 0; gi < ng; ++gi) {
+                    int tok = blk.row_token(p.a0 + g_first + gi, un.k);
+                    tma_load_4d(q_s + gi * RG * 128, &tq, &bars->q_full, 0, hd, tok, b);
+                    tma_load_4d(q_s + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full, 64, hd, tok, b);
+                }
+                for (int i = 0; i < un.n_it; ++i, ++g) {
+                    const int s = g % kStages;
+                    if (g >= kStages && !mbar_wait(&bars->kv_empty[s], ((g / kStages) - 1) & 1)) { fail(11); break; }
+                    const int tok = ((un.f_begin + i) * b1 + un.k) * b2;
+                    unsigned char* st = kv_s + s * kStageBytes;
+                    TRACE(0, g, 0);
+                    mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(4 * kHalf));
+                    tma_load_4d(st, &tk, &bars->kv_full[s], 0, hd, tok, b);
+                    tma_load_4d(st + kHalf, &tk, &bars->kv_full[s], 64, hd, tok, b);
+                    tma_load_4d(st + 2 * kHalf, &tv, &bars->kv_full[s], 0, hd, tok, b);
+                    tma_load_4d(st + 3 * kHalf, &tv, &bars->kv_full[s], 64, hd, tok, b);
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc_s = idesc_bf16(kTileRows, n_s, 0, 0);
-            const uint32_t idesc_o = idesc_bf16(kTileRows, kHeadDim, 0, 1);
-            const uint32_t q_addr = smem_addr(q_s);
-            const int ksteps_pv = n_s / 16;
-            auto issue_s = [&](int i) -> bool {
-                const int s = i % kStages;
-                if (!mbar_wait(&bars->kv_full[s], (i / kStages) & 1)) { fail(21); return false; }
+            constexpr uint32_t idesc_s = idesc_bf16(kTileRows, N_S, 0, 0);
+            constexpr uint32_t idesc_o = idesc_bf16(kTileRows, 2 * kHeadDim, 0, 1);
+            constexpr int ksteps_pv = N_S / 16;
+            // Descriptors differ from step to step only in the start-address field (16-byte units
+            // in the low word), so they are built once and advanced with integer adds.
+            const uint64_t q_desc = smem_desc_sw128(smem_addr(q_s), 16, 1024);
+            uint64_t k_desc[kStages], kv_desc_mn[kStages];
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) {
+                const uint32_t addr = smem_addr(kv_s + s * kStageBytes);
+                k_desc[s] = smem_desc_sw128(addr, 16, 1024);
+                kv_desc_mn[s] = smem_desc_sw128(addr, kHalf, 1024);   // 4 column blocks: K lo, K hi, V lo, V hi
+            }
+            auto pick = [&](const uint64_t (&d)[kStages], int s) { return s == 0 ? d[0] : (s == 1 ? d[1] : d[2]); };
+            auto issue_s = [&](int g) -> bool {
+                const int s = g % kStages;
+                if (!mbar_wait(&bars->kv_full[s], (g / kStages) & 1)) { fail(21); return false; }
                 tc_fence_after();
-                const uint32_t k_addr = smem_addr(kv_s + s * kStageBytes);
-                const uint32_t d = tmem + ((i & 1) ? kColS1 : kColS0);
+                const uint64_t kd = pick(k_desc, s);
+                const uint32_t d = tmem + ((g & 1) ? kColS1 : kColS0);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    uint32_t qa = q_addr + (ks >> 2) * (kTileRows * 128) + (ks & 3) * 32;
-                    uint32_t ka = k_addr + (ks >> 2) * (n_s * 128) + (ks & 3) * 32;
-                    mma_ss(d, smem_desc_sw128(qa, 16, 1024), smem_desc_sw128(ka, 16, 1024), idesc_s, ks > 0);
+                    const uint32_t q_off = ((ks >> 2) * (kTileRows * 128) + (ks & 3) * 32) >> 4;
+                    const uint32_t k_off = ((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
+                    mma_ss(d, q_desc + q_off, kd + k_off, idesc_s, ks > 0);
                 }
-                mma_commit(&bars->s_full[i & 1]);
+                mma_commit(&bars->s_full[g & 1]);
                 return true;
             };
-            bool ok = mbar_wait(&bars->q_full, 0);
-            if (!ok) fail(20);
-            ok = ok && issue_s(0);
-            for (int i = 0; ok && i < n_it && !bars->abort_flag; ++i) {
-                if (i + 1 < n_it && !issue_s(i + 1)) break;
-                if (!mbar_wait(&bars->p_full[i & 1], (i >> 1) & 1)) { fail(22); break; }
-                if (i > 0 && !mbar_wait(&bars->o_free, (i - 1) & 1)) { fail(23); break; }
-                tc_fence_after();
-                const int s = i % kStages;
-                const uint32_t k_addr = smem_addr(kv_s + s * kStageBytes);
-                const uint32_t v_addr = k_addr + kKVTileBytes;
-                const uint32_t p_t = tmem + ((i & 1) ? kColS1 : kColS0);
-                for (int kk = 0; kk < ksteps_pv; ++kk) {
-                    mma_ts(tmem + kColOK, p_t + kk * 8, smem_desc_sw128(k_addr + kk * 2048, n_s * 128, 1024), idesc_o, kk > 0);
-                    mma_ts(tmem + kColOV, p_t + kk * 8, smem_desc_sw128(v_addr + kk * 2048, n_s * 128, 1024), idesc_o, kk > 0);
+            int g = 0, uc = 0;
+            bool ok = true;
+            for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+                const RUnit un = decode_unit(rp, u);
+                if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
+                ok = issue_s(g);
+                if (ok && un.n_it == 1) mma_commit(&bars->q_empty);
+                for (int i = 0; ok && i < un.n_it; ++i, ++g) {
+                    if (i + 1 < un.n_it) {
+                        if (!issue_s(g + 1)) { ok = false; break; }
+                        if (i + 2 == un.n_it) mma_commit(&bars->q_empty);   // last read of this unit's Q tile
+                    }
+                    TRACE(1, g, 0);
+                    if (!mbar_wait(&bars->p_full[g & 1], (g >> 1) & 1)) { fail(22); ok = false; break; }
+                    TRACE(1, g, 1);
+                    if (g > 0 && !mbar_wait(&bars->o_free, (g - 1) & 1)) { fail(23); ok = false; break; }
+                    TRACE(1, g, 2);
+                    tc_fence_after();
+                    const int s = g % kStages;
+                    const uint64_t bd = pick(kv_desc_mn, s);
+                    const uint32_t p_t = tmem + ((g & 1) ? kColS1 : kColS0);
+#pragma unroll
+                    for (int kk = 0; kk < ksteps_pv; ++kk)
+                        mma_ts(tmem + kColO, p_t + kk * 8, bd + ((kk * 2048) >> 4), idesc_o, kk > 0);
+                    mma_commit(&bars->o_full);
+                    mma_commit(&bars->kv_empty[s]);
+                    TRACE(1, g, 3);
                 }
-                mma_commit(&bars->o_full);
-                mma_commit(&bars->kv_empty[s]);
             }
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------------ softmax warpgroup
+    } else if (warp >= 4 && warp < 12) {
+        // ------------------------------------------------------------------ softmax warpgroups
+        const int wg = (warp - 4) >> 2;                 // 0: even steps / buffer 0, 1: odd steps / buffer 1
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;               // tile row == TMEM lane
-        const bool warp_active = quad * 32 < valid_rows;
-        const int g = row / RG, j = row - g * RG;
-        const bool row_ok = g < ng && j < b2;
-        const long long aj = ((long long)bhl * p.na + g_first + g) * b2 + j;
+        const int gl = row / RG, j = row - gl * RG;
         const float scale_l2 = p.mult0 * kLog2e;
-        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
-        for (int i = 0; i < n_it && !bars->abort_flag; ++i) {
-            if (!mbar_wait(&bars->s_full[i & 1], (i >> 1) & 1)) { fail(31); break; }
-            tc_fence_after();
-            if (warp_active) {
-                const uint32_t s_t = tmem + lane_sel + ((i & 1) ? kColS1 : kColS0);
-                uint32_t raw[64];
-                if (n_s > 32) {
-                    tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
-                    tmem_ld32(s_t + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
-                } else if (n_s > 16) {
-                    tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
-                } else {
-                    tmem_ld16(s_t, *reinterpret_cast<uint32_t(*)[16]>(&raw[0]));
-                }
-                tmem_wait_ld();
-                float mx = -INFINITY;
+        const uint32_t s_t = tmem + ((uint32_t)(quad * 32) << 16) + (wg ? kColS1 : kColS0);
+        int g = 0;
+        bool ok = true;
+        for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
+            const RUnit un = decode_unit(rp, u);
+            const int g_first = un.tile * rp.groups_per_tile;
+            const int ng = min(rp.groups_per_tile, p.na - g_first);
+            const bool warp_active = quad * 32 < ng * RG;
+            const bool row_ok = gl < ng && j < b2;
+            const long long aj = ((long long)un.bhl * p.na + g_first + gl) * b2 + j;
+            for (int i = 0; i < un.n_it; ++i, ++g) {
+                if ((g & 1) != wg) continue;
+                if (lane == 0 && quad == 0) TRACE(2, g, 0);
+                if (!mbar_wait(&bars->s_full[wg], (g >> 1) & 1)) { fail(31); ok = false; break; }
+                tc_fence_after();
+                if (lane == 0 && quad == 0) TRACE(2, g, 1);
+                if (warp_active) {
+                    uint32_t raw[N_S];
+                    if constexpr (N_S == 64) {
+                        tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+                        tmem_ld32(s_t + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+                    } else if constexpr (N_S == 32) {
+                        tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+                    } else if constexpr (N_S == 48) {
+                        tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+                        tmem_ld16(s_t + 32, *reinterpret_cast<uint32_t(*)[16]>(&raw[32]));
+                    } else {
+                        tmem_ld16(s_t, *reinterpret_cast<uint32_t(*)[16]>(&raw[0]));
+                    }
+                    tmem_wait_ld();
+                    if (lane == 0 && quad == 0) TRACE(6, g, 0);
+                    // only the last 16 columns can lie beyond b2
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    float x = (c < b2) ? __uint_as_float(raw[c]) * scale_l2 : -INFINITY;
-                    raw[c] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
-                }
-                float z = 0.f, ent = 0.f;
+                    for (int c = N_S - 16; c < N_S; ++c)
+                        if (c >= b2) raw[c] = 0xff800000u;   // -inf
+                    float mx = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    float d = __uint_as_float(raw[c]) - mx;
-                    float e = exp2f(d);
-                    z += e;
-                    ent += (c < b2) ? e * d : 0.f;
-                    raw[c] = __float_as_uint(e);
-                }
-                const float inv_z = 1.0f / z;
-                uint32_t pk[32];
+                    for (int c = 0; c < N_S; ++c) mx = fmaxf(mx, __uint_as_float(raw[c]));
+                    const float neg_m = -mx * scale_l2;
+                    float z = 0.f, ent = 0.f;
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    pk[c] = pack_bf16(__uint_as_float(raw[2 * c]) * inv_z, __uint_as_float(raw[2 * c + 1]) * inv_z);
-                if (n_s > 32) {
-                    tmem_st32(s_t, pk);
-                } else if (n_s > 16) {
-                    tmem_st16(s_t, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
-                } else {
-                    uint32_t p8[16];
+                    for (int c = 0; c < N_S; ++c) {
+                        float d = fmaf(__uint_as_float(raw[c]), scale_l2, neg_m);   // log2 units, <= 0 (-inf if masked)
+                        float e = exp2f(d);
+                        z += e;
+                        ent = fmaf(e, fmaxf(d, -1e30f), ent);                        // masked: 0 * (-1e30) = 0
+                        raw[c] = __float_as_uint(e);
+                    }
+                    const float inv_z = 1.0f / z;
+                    if (lane == 0 && quad == 0) TRACE(6, g, 1);
+                    uint32_t pk[N_S / 2];
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) p8[c] = c < 8 ? pk[c] : 0u;
-                    tmem_st16(s_t, p8);   // 8 packed columns are used; the other 8 belong to no operand
+                    for (int c = 0; c < N_S / 2; ++c)
+                        pk[c] = pack_bf16_alu(__uint_as_float(raw[2 * c]) * inv_z, __uint_as_float(raw[2 * c + 1]) * inv_z);
+                    if constexpr (N_S == 64) {
+                        tmem_st32(s_t, pk);
+                    } else if constexpr (N_S == 32) {
+                        tmem_st16(s_t, pk);
+                    } else if constexpr (N_S == 48) {
+                        tmem_st16(s_t, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+                        uint32_t p2[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) p2[c] = c < 8 ? pk[16 + c] : 0u;
+                        tmem_st16(s_t + 16, p2);
+                    } else {
+                        uint32_t p2[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) p2[c] = c < 8 ? pk[c] : 0u;
+                        tmem_st16(s_t, p2);   // 8 packed columns are the operand; the other 8 lie inside the S buffer
+                    }
+                    tmem_wait_st();
+                    if (lane == 0 && quad == 0) TRACE(6, g, 2);
+                    if (row_ok) {
+                        const int key = (un.f_begin + i) * b1 + un.k;
+                        p.cL[aj * p.n_keys + key] = 0.6931471805599453f * ent * inv_z - __logf(z);
+                    }
                 }
-                tmem_wait_st();
-                if (row_ok) {
-                    const int key = (f_begin + i) * b1 + k;
-                    p.cL[aj * p.n_keys + key] = 0.6931471805599453f * ent * inv_z - __logf(z);
-                }
+                tc_fence_before();
+                mbar_arrive(&bars->p_full[wg]);
+                if (lane == 0 && quad == 0) TRACE(2, g, 2);
             }
-            tc_fence_before();
-            mbar_arrive(&bars->p_full[i & 1]);
         }
-    } else {
-        // ------------------------------------------------------------------ epilogue warpgroup
+    } else if (warp >= 12) {
+        // ------------------------------------------------------------------ epilogue warpgroups
+        const int which = (warp - 12) >> 2;              // 0: aL (columns 0..127 of O), 1: Y (columns 128..255)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        const bool warp_active = quad * 32 < valid_rows;
-        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
-        const bool issuer = (warp == 6 && lane == 0);
-        for (int i = 0; i < n_it && !bars->abort_flag; ++i) {
-            if (!mbar_wait(&bars->o_full, i & 1)) { fail(41); break; }
-            tc_fence_after();
-            if (i > 0) {                                  // staging buffer free again?
-                if (issuer) tma_store_wait_read<0>();
-                named_bar_sync(1, 128);
-            }
-            if (warp_active) {
-#pragma unroll 1
-                for (int which = 0; which < 2; ++which) {
-                    const uint32_t o_t = tmem + lane_sel + (which ? kColOV : kColOK);
-                    unsigned char* dst = stg_s + which * kQBytes + row * 128;
+        const uint32_t o_t = tmem + ((uint32_t)(quad * 32) << 16) + kColO + which * kHeadDim;
+        unsigned char* const dst = stg_s + which * kQBytes + row * 128;
+        int g = 0;
+        bool ok = true;
+        for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
+            const RUnit un = decode_unit(rp, u);
+            const int g_first = un.tile * rp.groups_per_tile;
+            const int ng = min(rp.groups_per_tile, p.na - g_first);
+            const bool warp_active = quad * 32 < ng * RG;
+            for (int i = 0; ok && i < un.n_it; ++i, ++g) {
+                if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 0);
+                if (!mbar_wait(&bars->o_full, g & 1)) { fail(41); ok = false; break; }
+                tc_fence_after();
+                if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 1);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(o_t + c * 32, r);
+                for (int h = 0; h < 2; ++h) {                 // 64 columns -> staging slot h
+                    if (g > 0 && !mbar_wait(&bars->stg_free[which][h], (g - 1) & 1)) { fail(42); ok = false; break; }
+                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 0);
+                    uint32_t ra[32], rb[32];
+                    if (warp_active) {
+                        tmem_ld32(o_t + h * 64, ra);
+                        tmem_ld32(o_t + h * 64 + 32, rb);
                         tmem_wait_ld();
-                        unsigned char* half = dst + (c >> 1) * (kTileRows * 128);
+                    }
+                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 1);
+                    if (h == 1) {
+                        tc_fence_before();
+                        mbar_arrive(&bars->o_free);            // accumulator may be overwritten from here on
+                        if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 2);
+                    }
+                    if (warp_active) {
+                        unsigned char* half = dst + h * (kTileRows * 128);
 #pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
-                            uint4 v;
-                            v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-                            v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-                            v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-                            v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-                            const int chunk = (c & 1) * 4 + ch;
-                            *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = v;
+                        for (int c = 0; c < 2; ++c) {
+                            const uint32_t (&r)[32] = c ? rb : ra;
+#pragma unroll
+                            for (int ch = 0; ch < 4; ++ch) {
+                                uint4 v;
+                                v.x = pack_bf16_alu(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+                                v.y = pack_bf16_alu(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+                                v.z = pack_bf16_alu(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+                                v.w = pack_bf16_alu(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+                                *reinterpret_cast<uint4*>(half + (((c * 4 + ch) ^ (row & 7)) << 4)) = v;
+                            }
                         }
+                    }
+                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 2);
+                    fence_async_smem();
+                    mbar_arrive(&bars->stg_full[which][h]);
+                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 3);
+                }
+                if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 3);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ TMA store issuers (warps 2, 3)
+        const int which = warp - 2;
+        if (lane == 0) {
+            const CUtensorMap* const tmap = which ? &ty : &tal;
+            unsigned char* const stg = stg_s + which * kQBytes;
+            int g = 0;
+            bool ok = true;
+            for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
+                const RUnit un = decode_unit(rp, u);
+                const int g_first = un.tile * rp.groups_per_tile;
+                const int ng = min(rp.groups_per_tile, p.na - g_first);
+                for (int i = 0; ok && i < un.n_it; ++i, ++g) {
+                    const int key = (un.f_begin + i) * b1 + un.k;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (!mbar_wait(&bars->stg_full[which][h], g & 1)) { fail(51); ok = false; break; }
+                        for (int gi = 0; gi < ng; ++gi) {
+                            const int aj0 = (un.bhl * p.na + g_first + gi) * b2;
+                            tma_store_3d(tmap, stg + h * (kTileRows * 128) + gi * RG * 128, h * 64, key, aj0);
+                        }
+                        tma_store_commit();
+                        // all groups but the newest have been read: the other slot may be refilled
+                        tma_store_wait_read<1>();
+                        if (g > 0 || h == 1) mbar_arrive(&bars->stg_free[which][h ^ 1]);
                     }
                 }
             }
-            tc_fence_before();
-            mbar_arrive(&bars->o_free);
-            fence_async_smem();
-            named_bar_sync(1, 128);
-            if (issuer) {
-                const int key = (f_begin + i) * b1 + k;
-                for (int g = 0; g < ng; ++g) {
-                    const int aj0 = (bhl * p.na + g_first + g) * b2;
-                    const unsigned char* src = stg_s + g * RG * 128;
-                    tma_store_3d(&tal, src, 0, key, aj0);
-                    tma_store_3d(&tal, src + kTileRows * 128, 64, key, aj0);
-                    tma_store_3d(&ty, src + kQBytes, 0, key, aj0);
-                    tma_store_3d(&ty, src + kQBytes + kTileRows * 128, 64, key, aj0);
-                }
-                tma_store_commit();
-            }
+            tma_store_wait_all<0>();
         }
-        if (issuer) tma_store_wait_all<0>();
     }
 
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+#ifdef SFM_TRACE
+    if (rp.trace && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < 8 * 32 * 4; i += blockDim.x) rp.trace[i] = trace_s[i];
+#endif
 }
 
 }  // namespace
 
-// Launches the tensor-core row step for one chunk.  `status` is a device int the kernel sets on an
-// internal timeout.
+#ifdef SFM_TRACE
+long long* g_sfm_trace = nullptr;
+extern "C" void sfm_debug_set_trace(long long* p) { g_sfm_trace = p; }
+#endif
+
+// Launches the tensor-core row step for one chunk as a persistent grid.  `status` is a device int the
+// kernel sets on an internal timeout.
 int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q,k,v,aL,Y */, int rows_per_group, int n_s,
-                     int* status, cudaStream_t s) {
+                     int* status, int num_sms, cudaStream_t s) {
     LaunchScope scope(kClsRStep, s);
     RTcParams rp;
     rp.mp = p;
     rp.rows_per_group = rows_per_group;
     rp.groups_per_tile = kTileRows / rows_per_group;
-    rp.n_s = n_s;
+    rp.tiles = (p.na + rp.groups_per_tile - 1) / rp.groups_per_tile;
+    rp.n_units = p.nbh * rp.tiles * p.blk.b1 * p.fsplit;
     rp.status = status;
-    int tiles = (p.na + rp.groups_per_tile - 1) / rp.groups_per_tile;
-    dim3 grid(p.blk.b1 * p.fsplit, tiles, p.nbh);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(monarch_r_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+#ifdef SFM_TRACE
+    rp.trace = g_sfm_trace;
+#endif
+    dim3 grid(rp.n_units < num_sms ? rp.n_units : num_sms);
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], rp);
+        return 0;
+    };
+    int rc;
+    switch (n_s) {
+        case 16: rc = go(monarch_r_tc_kernel<16>); break;
+        case 32: rc = go(monarch_r_tc_kernel<32>); break;
+        case 48: rc = go(monarch_r_tc_kernel<48>); break;
+        case 64: rc = go(monarch_r_tc_kernel<64>); break;
+        default: return SFM_ERR_UNSUPPORTED;
     }
-    monarch_r_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], rp);
+    if (rc) return rc;
     return (int)cudaGetLastError();
 }
 
