@@ -10,11 +10,12 @@ using namespace sfm;
 namespace sfm {
 int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps, int rows_per_group, int n_s, int* status,
                      int num_sms, cudaStream_t s);
+int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps, int* status, int num_sms, cudaStream_t s);
 }
 
 namespace {
 
-constexpr size_t kDefaultBridgeBudget = 64ull << 20;   // bytes of row-step results kept per chunk
+constexpr size_t kDefaultBridgeBudget = 1ull << 30;    // bytes of row-step results kept per chunk
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
@@ -131,7 +132,7 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
         const uint64_t n_aj = (uint64_t)pl.nbh_chunk * pl.na_chunk * pl.blk.b2;
         uint64_t db[3] = {(uint64_t)kHeadDim, (uint64_t)pl.n_keys, n_aj};
         uint64_t sb[2] = {row, (uint64_t)pl.n_keys * row};
-        uint32_t bb[3] = {64, 1, (uint32_t)pl.blk.b2};
+        uint32_t bb[3] = {64, 128, 1};   // column step: 128 keys of one (query group, column) per load
         if ((rc = make_tmap_bf16(&maps[0], q, 4, dq, sq, bq))) return rc;
         if ((rc = make_tmap_bf16(&maps[1], kc, 4, dk, sk, bk))) return rc;
         if ((rc = make_tmap_bf16(&maps[2], vc, 4, dk, sk, bk))) return rc;
@@ -168,7 +169,9 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                     if ((rc = launch_r_step(p, stream))) return rc;
                 }
                 if (last) {
-                    if ((rc = launch_l_step(p, 0, stream))) return rc;
+                    if (use_tc && pl.blk.b1 <= 128) {
+                        if ((rc = launch_l_step_tc(p, maps + 3, status, num_sms, stream))) return rc;
+                    } else if ((rc = launch_l_step(p, 0, stream))) return rc;
                 } else {
                     if ((rc = launch_l_step(p, 1, stream))) return rc;
                     if ((rc = launch_l_iter(p, stream))) return rc;

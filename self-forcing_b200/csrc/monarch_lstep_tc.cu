@@ -1,0 +1,404 @@
+// Monarch column step on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+// One unit = (batch*head, query group a, column j): the b1 queries Q[a,:,j] attend the n_keys = F*b1
+// summary keys aL[a,f,j,k] (bias -cL, values Y) produced by the row step.  CTAs are persistent and
+// walk the unit list with a fixed stride.  Keys stream through shared memory in tiles of 128:
+//   S = Q_tile aL_tile^T            tcgen05.mma, both operands from shared memory (K-major)
+//   P = exp2(scale*S - cL - m)      one thread per query row, running max m / sum l in registers
+//   O += P Y_tile                   tcgen05.mma, A = P (bf16) from TMEM, B = Y tile (MN-major)
+// Even and odd tiles of a unit go to two softmax warpgroups with their own S/P buffer and their own
+// accumulator (split-KV); the epilogue warpgroup merges the two partial results, normalises and
+// writes the unit's output rows to natural token order with 32-byte stores.
+//
+// The 128-row MMA tile is much taller than b1 (30 at 480p framewise), so query row i is placed on
+// tile row (i mod 4)*32 + i/4: the four warps of a warpgroup (one per TMEM lane quadrant) then
+// share the softmax work.  The other tile rows hold stale data and are never read back.
+//
+// Warp roles (16 warps): 0 = producer (TMA tiles, bias slices, query gather), 1 = PV-GEMM issuer (owns the
+// TMEM allocation), 2 = S-GEMM issuer, 3 idle, 4..7 / 8..11 = softmax warpgroups (even / odd tiles),
+// 12..15 = epilogue warpgroup.  Every wait is bounded; a timeout records a status code.
+//
+// Arithmetic follows monarch_attn_ref_op (wan/modules/monarch_attn.py:1821-1829).
+#include "monarch_params.cuh"
+#include "profile.cuh"
+#include "tc05.cuh"
+
+namespace sfm {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kAStages = 2;                // aL tile ring (released as soon as the S GEMM has read it)
+constexpr int kYStages = 3;                // (Y tile, cL slice) ring (released after the PV GEMM)
+constexpr int kThreads = 512;
+constexpr int kKT = 128;                   // keys per tile
+constexpr uint32_t kTmemCols = 512;
+// TMEM columns: S / P buffers of the two softmax warpgroups at 0 and 128, their accumulators at 256 and 384
+__host__ __device__ constexpr uint32_t col_s(int w) { return (uint32_t)w * 128u; }
+__host__ __device__ constexpr uint32_t col_o(int w) { return 256u + (uint32_t)w * 128u; }
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: accumulators are rescaled only past this growth
+
+struct LTcParams {
+    MonarchParams mp;
+    int n_units;     // nbh * na * b2
+    int* status;
+};
+
+struct __align__(8) Barriers {
+    uint64_t q_full, q_empty;
+    uint64_t a_full[kAStages], a_empty[kAStages];
+    uint64_t y_full[kYStages], y_empty[kYStages];
+    uint64_t s_full[2], p_full[2], sp_free[2];
+    uint64_t pv_done[2];                   // all PV GEMMs issued so far into accumulator w have completed
+    uint64_t o_full, o_free;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float stats[2][2][128];                // [warpgroup][m | l][tile row]
+    float cl[kYStages][kKT];               // bias slices travelling with the Y ring
+};
+
+constexpr int kQBytes = 2 * 128 * 128;     // query tile, two 64-column halves
+constexpr int kTileBytes = 2 * kKT * 128;  // aL or Y tile
+constexpr int kSmemBytes = 1024 + kQBytes + (kAStages + kYStages) * kTileBytes + (int)sizeof(Barriers) + 64;
+
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
+struct LUnit { int bhl, al, j; };
+__device__ __forceinline__ LUnit decode_unit(const MonarchParams& p, int u) {
+    LUnit r;
+    r.j = u % p.blk.b2; u /= p.blk.b2;
+    r.al = u % p.na;
+    r.bhl = u / p.na;
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_constant__ CUtensorMap ty, LTcParams lp) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = base;
+    unsigned char* a_s = q_s + kQBytes;
+    unsigned char* y_s = a_s + kAStages * kTileBytes;
+    Barriers* bars = reinterpret_cast<Barriers*>(y_s + kYStages * kTileBytes);
+
+    const MonarchParams& p = lp.mp;
+    const Blocking& blk = p.blk;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b1 = blk.b1, b2 = blk.b2;
+    const int n_keys = p.n_keys;
+    const int n_tiles = (n_keys + kKT - 1) / kKT;
+    const long long tok_pitch = (long long)p.H * kHeadDim;
+
+    if (tid == 0) {
+        mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->q_empty, 1);
+        for (int s = 0; s < kAStages; ++s) { mbar_init(&bars->a_full[s], 1); mbar_init(&bars->a_empty[s], 1); }
+        for (int s = 0; s < kYStages; ++s) { mbar_init(&bars->y_full[s], 1); mbar_init(&bars->y_empty[s], 1); }
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(&bars->s_full[w], 1); mbar_init(&bars->p_full[w], 128);
+            mbar_init(&bars->sp_free[w], 1); mbar_init(&bars->pv_done[w], 1);
+        }
+        mbar_init(&bars->o_full, 1);
+        mbar_init(&bars->o_free, 128);
+        bars->abort_flag = 0;
+        mbar_init_fence();
+    }
+    // rows of the query tile that no unit writes must still hold finite numbers
+    for (int i = tid; i < kQBytes / 16; i += kThreads) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+    if (warp == 1) { tmem_alloc(&bars->tmem_base, kTmemCols); tmem_relinquish(); }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    auto fail = [&](int code) {
+        bars->abort_flag = 1;
+        atomicCAS(lp.status, 0, code);
+    };
+    const int u_first = blockIdx.x, u_stride = gridDim.x;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) { prefetch_tmap(&tal); prefetch_tmap(&ty); }
+        int g = 0, uc = 0;
+        bool ok = true;
+        for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+            const LUnit un = decode_unit(p, u);
+            const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
+            const int a_abs = p.a0 + un.al;
+            const int aj = (un.bhl * p.na + un.al) * b2 + un.j;
+            // queries: row i -> tile row (i & 3) * 32 + (i >> 2), 128-byte swizzled halves
+            if (uc > 0) {
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(&bars->q_empty, (uc - 1) & 1) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(10); break; }
+            }
+            const __nv_bfloat16* qb = p.q + (long long)b * p.q_bs + (long long)hd * kHeadDim;
+            for (int idx = lane; idx < b1 * 16; idx += 32) {
+                const int i = idx >> 4, ch = idx & 15;
+                const uint4 val = *reinterpret_cast<const uint4*>(qb + (blk.row_token(a_abs, i) + un.j) * tok_pitch + ch * 8);
+                const int r = (i & 3) * 32 + (i >> 2);
+                *reinterpret_cast<uint4*>(q_s + (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = val;
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->q_full);
+            // key tiles: aL into its ring, then Y + the bias slice into theirs
+            for (int t = 0; t < n_tiles; ++t, ++g) {
+                const int sa = g % kAStages, sy = g % kYStages;
+                int okw = 1;
+                if (lane == 0 && g >= kAStages) okw = mbar_wait(&bars->a_empty[sa], ((g / kAStages) - 1) & 1) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(11); ok = false; break; }
+                if (lane == 0) {
+                    unsigned char* at = a_s + sa * kTileBytes;
+                    mbar_arrive_expect_tx(&bars->a_full[sa], (uint32_t)kTileBytes);
+                    tma_load_3d(at, &tal, &bars->a_full[sa], 0, t * kKT, aj);
+                    tma_load_3d(at + kKT * 128, &tal, &bars->a_full[sa], 64, t * kKT, aj);
+                }
+                if (lane == 0 && g >= kYStages) okw = mbar_wait(&bars->y_empty[sy], ((g / kYStages) - 1) & 1) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(12); ok = false; break; }
+                const float* csrc = p.cL + (long long)aj * n_keys + t * kKT;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = t * kKT + lane * 4 + e;
+                    bars->cl[sy][lane * 4 + e] = key < n_keys ? csrc[lane * 4 + e] * kLog2e : INFINITY;   // +inf masks the key
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    unsigned char* yt = y_s + sy * kTileBytes;
+                    mbar_arrive_expect_tx(&bars->y_full[sy], (uint32_t)kTileBytes);
+                    tma_load_3d(yt, &ty, &bars->y_full[sy], 0, t * kKT, aj);
+                    tma_load_3d(yt + kKT * 128, &ty, &bars->y_full[sy], 64, t * kKT, aj);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ S-GEMM issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16(128, kKT, 0, 0);
+            const uint64_t q_desc = smem_desc_sw128(smem_addr(q_s), 16, 1024);
+            const uint64_t a_desc0 = smem_desc_sw128(smem_addr(a_s), 16, 1024);
+            int g = 0, uc = 0, cnt[2] = {0, 0};   // cnt[w]: tiles given to warpgroup w so far
+            bool ok = true;
+            for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+                if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
+                for (int t = 0; t < n_tiles; ++t, ++g) {
+                    const int sa = g % kAStages, w = t & 1;
+                    const int idx = cnt[w]++;
+                    if (!mbar_wait(&bars->a_full[sa], (g / kAStages) & 1)) { fail(21); ok = false; break; }
+                    if (idx >= 1 && !mbar_wait(&bars->sp_free[w], (idx - 1) & 1)) { fail(25); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t ad = a_desc0 + (uint64_t)((sa * kTileBytes) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;   // same geometry for both tiles
+                        mma_ss(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0);
+                    }
+                    mma_commit(&bars->s_full[w]);
+                    mma_commit(&bars->a_empty[sa]);
+                    if (t + 1 == n_tiles) mma_commit(&bars->q_empty);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ PV-GEMM issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = idesc_bf16(128, kHeadDim, 0, 1);
+            const uint64_t y_desc0 = smem_desc_sw128(smem_addr(y_s), kKT * 128, 1024);
+            int g = 0, uc = 0, cnt[2] = {0, 0};
+            bool ok = true;
+            for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+                for (int t = 0; t < n_tiles; ++t, ++g) {
+                    const int sy = g % kYStages, w = t & 1;
+                    const int idx = cnt[w]++;
+                    if (!mbar_wait(&bars->p_full[w], idx & 1)) { fail(22); ok = false; break; }
+                    if (!mbar_wait(&bars->y_full[sy], (g / kYStages) & 1)) { fail(26); ok = false; break; }
+                    // first GEMM of the unit into this accumulator overwrites it: the previous unit's
+                    // result must have been read
+                    if (t < 2 && uc > 0 && !mbar_wait(&bars->o_free, (uc - 1) & 1)) { fail(23); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t yd = y_desc0 + (uint64_t)((sy * kTileBytes) >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < kKT / 16; ++kk)
+                        mma_ts(tmem + col_o(w), tmem + col_s(w) + kk * 8, yd + ((kk * 2048) >> 4), idesc_o, (t >= 2) || (kk > 0));
+                    mma_commit(&bars->pv_done[w]);
+                    mma_commit(&bars->y_empty[sy]);
+                    mma_commit(&bars->sp_free[w]);
+                    if (t + 1 == n_tiles) mma_commit(&bars->o_full);
+                }
+            }
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ------------------------------------------------------------------ softmax warpgroups
+        const int w = (warp - 4) >> 2;
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        const uint32_t s_t = tmem + lane_sel + col_s(w);
+        const uint32_t o_t = tmem + lane_sel + col_o(w);
+        const float scale_l2 = p.scale * kLog2e;
+        int g = 0, uc = 0, idx = 0;           // idx: tiles this warpgroup has handled so far
+        bool ok = true;
+        for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+            float m_run = -INFINITY, l_run = 0.f;
+            int my_tiles = 0;
+            for (int t = 0; t < n_tiles; ++t, ++g) {
+                if ((t & 1) != w) continue;
+                const int sy = g % kYStages;
+                const float* cs = bars->cl[sy];
+                if (!mbar_wait(&bars->s_full[w], idx & 1)) { fail(31); ok = false; break; }
+                if (!mbar_wait(&bars->y_full[sy], (g / kYStages) & 1)) { fail(33); ok = false; break; }   // bias slice visible
+                tc_fence_after();
+                // pass 1: row maximum of the biased logits (log2 units)
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kKT; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(s_t + c0, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaf(__uint_as_float(r[c]), scale_l2, -cs[c0 + c]));
+                }
+                // lazy rescale: keep the old reference while the maximum grew by less than the threshold
+                bool rescale = false;
+                float corr = 1.0f;
+                if (my_tiles == 0) {
+                    m_run = mx;
+                } else if (mx > m_run + kRescaleThreshold) {
+                    corr = exp2f(m_run - mx);
+                    m_run = mx;
+                    l_run *= corr;
+                    rescale = true;
+                }
+                if (__any_sync(0xffffffffu, rescale)) {
+                    // the accumulator may only be touched once the previous GEMM into it has finished
+                    if (!mbar_wait(&bars->pv_done[w], (idx - 1) & 1)) { fail(32); ok = false; break; }
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(o_t + c0, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                        tmem_st32(o_t + c0, r);
+                    }
+                    tmem_wait_st();
+                }
+                const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                // pass 2: P = exp2(logit - m), packed bf16 written back over the S columns already consumed
+                float lsum = 0.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kKT; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(s_t + c0, r);
+                    tmem_wait_ld();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        float e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, -cs[c0 + c]) + neg_m);
+                        float e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, -cs[c0 + c + 1]) + neg_m);
+                        lsum += e0 + e1;
+                        pk[c >> 1] = pack_bf16_alu(e0, e1);
+                    }
+                    tmem_st16(s_t + (c0 >> 1), pk);
+                }
+                tmem_wait_st();
+                l_run += lsum;
+                ++my_tiles;
+                ++idx;
+                if (t + 2 >= n_tiles) {                   // this warpgroup's last tile of the unit: publish (m, l)
+                    // the previous unit's statistics must have been consumed
+                    if (uc > 0 && !mbar_wait(&bars->o_free, (uc - 1) & 1)) { fail(34); ok = false; break; }
+                    bars->stats[w][0][row] = m_run;
+                    bars->stats[w][1][row] = l_run;
+                }
+                tc_fence_before();
+                mbar_arrive(&bars->p_full[w]);
+            }
+        }
+    } else if (warp >= 12) {
+        // ------------------------------------------------------------------ epilogue warpgroup
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int i_row = lane * 4 + quad;
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        int uc = 0;
+        bool ok = true;
+        for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+            const LUnit un = decode_unit(p, u);
+            const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
+            if (!mbar_wait(&bars->o_full, uc & 1)) { fail(41); break; }
+            tc_fence_after();
+            // even tiles went to warpgroup 0, odd tiles to warpgroup 1
+            const bool has0 = true;
+            const bool has1 = n_tiles > 1;
+            const float m0 = has0 ? bars->stats[0][0][row] : -INFINITY, l0 = has0 ? bars->stats[0][1][row] : 0.f;
+            const float m1 = has1 ? bars->stats[1][0][row] : -INFINITY, l1 = has1 ? bars->stats[1][1][row] : 0.f;
+            const float ms = fmaxf(m0, m1);
+            const float w0 = has0 ? exp2f(m0 - ms) : 0.f;
+            const float w1 = has1 ? exp2f(m1 - ms) : 0.f;
+            const float inv = 1.0f / (w0 * l0 + w1 * l1);
+            const bool row_ok = i_row < b1;
+            __nv_bfloat16* out_row = nullptr;
+            if (row_ok) {
+                const long long tok = blk.row_token(p.a0 + un.al, i_row) + un.j;
+                out_row = p.out + (((long long)b * p.n_q + tok) * p.H + hd) * kHeadDim;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                uint32_t ra[32], rb[32];
+                tmem_ld32(tmem + lane_sel + col_o(0) + c0, ra);
+                tmem_ld32(tmem + lane_sel + col_o(1) + c0, rb);
+                tmem_wait_ld();
+                if (c0 + 32 == kHeadDim) {
+                    tc_fence_before();
+                    mbar_arrive(&bars->o_free);               // accumulators and statistics are in registers
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int v8 = 0; v8 < 2; ++v8) {
+                        uint32_t wv[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int c = v8 * 16 + 2 * e;
+                            float x0 = 0.f, x1 = 0.f;
+                            if (has0) { x0 = __uint_as_float(ra[c]) * w0; x1 = __uint_as_float(ra[c + 1]) * w0; }
+                            if (has1) { x0 = fmaf(__uint_as_float(rb[c]), w1, x0); x1 = fmaf(__uint_as_float(rb[c + 1]), w1, x1); }
+                            wv[e] = pack_bf16(x0 * inv, x1 * inv);
+                        }
+                        st_global_v8(out_row + c0 + v8 * 16, wv);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+
+// Launches the tensor-core column step for one chunk as a persistent grid.  maps = {aL, Y} with a
+// (64, 128 keys, 1) box.
+int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps, int* status, int num_sms, cudaStream_t s) {
+    LaunchScope scope(kClsLStep, s);
+    LTcParams lp;
+    lp.mp = p;
+    lp.n_units = p.nbh * p.na * p.blk.b2;
+    lp.status = status;
+    dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
+    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    monarch_l_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], lp);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace sfm

@@ -10,16 +10,15 @@
 //   [aL | Y] = P [K[f,k] | V[f,k]]       one N=256 tcgen05.mma per 16 keys, A = P from TMEM,
 //                                        B = the K and V tiles side by side (MN-major)
 //   cL = sum_l P ln P                    from the softmax registers
-// and streams aL, Y (bf16) to the chunk's bridge with TMA stores; cL goes out with plain stores.
+// and streams aL, Y (bf16) and cL to the chunk's bridge.
 //
-// Warp roles (20 warps): 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
-// 2..3 = TMA store issuers for the aL / Y halves of the accumulator,
+// Warp roles (20 warps): 0 = TMA producer, 1 = issuer of the [aL | Y] GEMMs (owns the TMEM
+// allocation), 2 = issuer of the S GEMMs, 3 idle,
 // 4..7 and 8..11 = two softmax warpgroups that take even / odd steps (each owns one of the two
 // S/P buffers in TMEM), 12..15 and 16..19 = two epilogue warpgroups (aL half / Y half of the
 // accumulator).  The S GEMM of step i+1 overlaps the softmax of step i; the output accumulator is
 // single buffered and handed back to the MMA warp as soon as both halves sit in registers.  Each
-// epilogue warpgroup converts its 128 columns in two 64-column halves into a two-slot staging ring
-// that its store-issuing warp drains with TMA, so conversion and stores overlap.  All roles run the same unit loop and meet
+// epilogue thread owns one bridge row and writes it straight from registers with 32-byte stores.  All roles run the same unit loop and meet
 // only through mbarriers whose phases follow running step counters, so the pipeline keeps flowing
 // across unit boundaries.  Every wait is bounded; on a timeout the CTA records a status code and
 // unwinds.
@@ -36,7 +35,7 @@ using namespace tc;
 
 namespace {
 
-constexpr int kStages = 3;            // K/V tile ring
+constexpr int kStages = 5;            // K/V tile ring
 constexpr int kThreads = 640;
 constexpr int kTileRows = 128;
 constexpr uint32_t kTmemCols = 512;
@@ -51,6 +50,7 @@ struct RTcParams {
     int* status;           // device status word (0 = ok)
 #ifdef SFM_TRACE
     long long* trace;      // debug build only: per-role, per-step cycle stamps of CTA 0
+    int ablate;            // debug build only: bit 0 skips the softmax arithmetic, bit 1 the stores, bit 2 the drains
 #endif
 };
 
@@ -58,6 +58,11 @@ struct RTcParams {
 #define TRACE(role, it, ev) do { if ((it) < 32) trace_s[((role) * 32 + (it)) * 4 + (ev)] = clock64(); } while (0)
 #else
 #define TRACE(role, it, ev) do {} while (0)
+#endif
+#ifdef SFM_TRACE
+#define ABLATE(bit) (rp.ablate & (bit))
+#else
+#define ABLATE(bit) 0
 #endif
 
 struct RUnit {
@@ -82,10 +87,9 @@ struct __align__(8) Barriers {
     uint64_t kv_empty[kStages];
     uint64_t s_full[2];
     uint64_t p_full[2];
+    uint64_t sp_free[2];       // PV GEMM has consumed the P operand held in S/P buffer 0 / 1
     uint64_t o_full;
     uint64_t o_free;
-    uint64_t stg_full[2][2];   // [tensor][slot]: 128 epilogue threads have filled the slot
-    uint64_t stg_free[2][2];   // [tensor][slot]: the TMA store has finished reading the slot
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -93,13 +97,18 @@ struct __align__(8) Barriers {
 // shared memory carve-up (bytes from a 1024-aligned base)
 constexpr int kQBytes = 2 * kTileRows * 128;               // two 64-column halves
 constexpr int kStageBytes = 4 * 64 * 128;                  // K half 0, K half 1, V half 0, V half 1 (<= 64 rows each)
-constexpr int kStagingBytes = 2 * kQBytes;                 // aL and Y, bf16, TMA-store source
-constexpr int kSmemBytes = 1024 + kQBytes + kStages * kStageBytes + kStagingBytes + 256;
+constexpr int kSmemBytes = 1024 + kQBytes + kStages * kStageBytes + 256;
 
 // Register budget per warpgroup (the kernel launches with 640 threads at 96 registers each): the
 // control warpgroup gives registers back, the compute warpgroups take more.
 template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// 32-byte store of 16 bf16 to global memory (pointer 32-byte aligned).
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
 
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -114,8 +123,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
     unsigned char* kv_s = q_s + kQBytes;
-    unsigned char* stg_s = kv_s + kStages * kStageBytes;
-    Barriers* bars = reinterpret_cast<Barriers*>(stg_s + kStagingBytes);
+    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + kStages * kStageBytes);
 
 #ifdef SFM_TRACE
     __shared__ long long trace_s[8 * 32 * 4];
@@ -134,10 +142,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         mbar_init(&bars->q_empty, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->s_full[s], 1); mbar_init(&bars->p_full[s], 128); }
+        for (int s = 0; s < 2; ++s) mbar_init(&bars->sp_free[s], 1);
         mbar_init(&bars->o_full, 1);
         mbar_init(&bars->o_free, 256);
-        for (int e = 0; e < 2; ++e)
-            for (int h = 0; h < 2; ++h) { mbar_init(&bars->stg_full[e][h], 128); mbar_init(&bars->stg_free[e][h], 1); }
         bars->abort_flag = 0;
         mbar_init_fence();
     }
@@ -172,6 +179,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStages;
+                    if (ABLATE(8)) continue;
                     if (g >= kStages && !mbar_wait(&bars->kv_empty[s], ((g / kStages) - 1) & 1)) { fail(11); break; }
                     const int tok = ((un.f_begin + i) * b1 + un.k) * b2;
                     unsigned char* st = kv_s + s * kStageBytes;
@@ -184,50 +192,48 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ S-GEMM issuer
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16(kTileRows, N_S, 0, 0);
-            constexpr uint32_t idesc_o = idesc_bf16(kTileRows, 2 * kHeadDim, 0, 1);
-            constexpr int ksteps_pv = N_S / 16;
             // Descriptors differ from step to step only in the start-address field (16-byte units
             // in the low word), so they are built once and advanced with integer adds.
             const uint64_t q_desc = smem_desc_sw128(smem_addr(q_s), 16, 1024);
-            uint64_t k_desc[kStages], kv_desc_mn[kStages];
-#pragma unroll
-            for (int s = 0; s < kStages; ++s) {
-                const uint32_t addr = smem_addr(kv_s + s * kStageBytes);
-                k_desc[s] = smem_desc_sw128(addr, 16, 1024);
-                kv_desc_mn[s] = smem_desc_sw128(addr, kHalf, 1024);   // 4 column blocks: K lo, K hi, V lo, V hi
-            }
-            auto pick = [&](const uint64_t (&d)[kStages], int s) { return s == 0 ? d[0] : (s == 1 ? d[1] : d[2]); };
-            auto issue_s = [&](int g) -> bool {
-                const int s = g % kStages;
-                if (!mbar_wait(&bars->kv_full[s], (g / kStages) & 1)) { fail(21); return false; }
-                tc_fence_after();
-                const uint64_t kd = pick(k_desc, s);
-                const uint32_t d = tmem + ((g & 1) ? kColS1 : kColS0);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t q_off = ((ks >> 2) * (kTileRows * 128) + (ks & 3) * 32) >> 4;
-                    const uint32_t k_off = ((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-                    mma_ss(d, q_desc + q_off, kd + k_off, idesc_s, ks > 0);
-                }
-                mma_commit(&bars->s_full[g & 1]);
-                return true;
-            };
+            const uint64_t k_desc0 = smem_desc_sw128(smem_addr(kv_s), 16, 1024);
             int g = 0, uc = 0;
             bool ok = true;
             for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
                 const RUnit un = decode_unit(rp, u);
                 if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
-                ok = issue_s(g);
-                if (ok && un.n_it == 1) mma_commit(&bars->q_empty);
-                for (int i = 0; ok && i < un.n_it; ++i, ++g) {
-                    if (i + 1 < un.n_it) {
-                        if (!issue_s(g + 1)) { ok = false; break; }
-                        if (i + 2 == un.n_it) mma_commit(&bars->q_empty);   // last read of this unit's Q tile
+                for (int i = 0; i < un.n_it; ++i, ++g) {
+                    const int s = g % kStages;
+                    if (!ABLATE(8) && !mbar_wait(&bars->kv_full[s], (g / kStages) & 1)) { fail(21); ok = false; break; }
+                    if (g >= 2 && !mbar_wait(&bars->sp_free[g & 1], ((g >> 1) - 1) & 1)) { fail(25); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t kd = k_desc0 + (uint64_t)((s * kStageBytes) >> 4);
+                    const uint32_t d = tmem + ((g & 1) ? kColS1 : kColS0);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t q_off = ((ks >> 2) * (kTileRows * 128) + (ks & 3) * 32) >> 4;
+                        const uint32_t k_off = ((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
+                        mma_ss(d, q_desc + q_off, kd + k_off, idesc_s, ks > 0);
                     }
+                    mma_commit(&bars->s_full[g & 1]);
+                    if (i + 1 == un.n_it) mma_commit(&bars->q_empty);   // last read of this unit's Q tile
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ PV-GEMM issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = idesc_bf16(kTileRows, 2 * kHeadDim, 0, 1);
+            constexpr int ksteps_pv = N_S / 16;
+            const uint64_t kv_desc_mn0 = smem_desc_sw128(smem_addr(kv_s), kHalf, 1024);   // 4 column blocks: K lo, K hi, V lo, V hi
+            int g = 0;
+            bool ok = true;
+            for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
+                const RUnit un = decode_unit(rp, u);
+                for (int i = 0; i < un.n_it; ++i, ++g) {
                     TRACE(1, g, 0);
                     if (!mbar_wait(&bars->p_full[g & 1], (g >> 1) & 1)) { fail(22); ok = false; break; }
                     TRACE(1, g, 1);
@@ -235,13 +241,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     TRACE(1, g, 2);
                     tc_fence_after();
                     const int s = g % kStages;
-                    const uint64_t bd = pick(kv_desc_mn, s);
+                    const uint64_t bd = kv_desc_mn0 + (uint64_t)((s * kStageBytes) >> 4);
                     const uint32_t p_t = tmem + ((g & 1) ? kColS1 : kColS0);
 #pragma unroll
                     for (int kk = 0; kk < ksteps_pv; ++kk)
                         mma_ts(tmem + kColO, p_t + kk * 8, bd + ((kk * 2048) >> 4), idesc_o, kk > 0);
                     mma_commit(&bars->o_full);
                     mma_commit(&bars->kv_empty[s]);
+                    mma_commit(&bars->sp_free[g & 1]);
                     TRACE(1, g, 3);
                 }
             }
@@ -269,7 +276,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 if (!mbar_wait(&bars->s_full[wg], (g >> 1) & 1)) { fail(31); ok = false; break; }
                 tc_fence_after();
                 if (lane == 0 && quad == 0) TRACE(2, g, 1);
-                if (warp_active) {
+                if (warp_active && !ABLATE(1)) {
                     uint32_t raw[N_S];
                     if constexpr (N_S == 64) {
                         tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
@@ -341,7 +348,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const uint32_t o_t = tmem + ((uint32_t)(quad * 32) << 16) + kColO + which * kHeadDim;
-        unsigned char* const dst = stg_s + which * kQBytes + row * 128;
         int g = 0;
         bool ok = true;
         for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
@@ -354,75 +360,42 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 if (!mbar_wait(&bars->o_full, g & 1)) { fail(41); ok = false; break; }
                 tc_fence_after();
                 if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 1);
+                // This thread's bridge row: 256 bytes at (aj, key), written as 32-byte vectors.
+                const int gl = row / RG, j = row - gl * RG;
+                const bool row_ok = warp_active && gl < ng && j < b2;
+                const long long aj = ((long long)un.bhl * p.na + g_first + gl) * b2 + j;
+                const int key = (un.f_begin + i) * b1 + un.k;
+                __nv_bfloat16* const out_row = (which ? p.Y : p.aL) + (aj * p.n_keys + key) * kHeadDim;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {                 // 64 columns -> staging slot h
-                    if (g > 0 && !mbar_wait(&bars->stg_free[which][h], (g - 1) & 1)) { fail(42); ok = false; break; }
-                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 0);
+                for (int h = 0; h < 2; ++h) {                 // 64 columns at a time
                     uint32_t ra[32], rb[32];
-                    if (warp_active) {
+                    if (warp_active && !ABLATE(4)) {
                         tmem_ld32(o_t + h * 64, ra);
                         tmem_ld32(o_t + h * 64 + 32, rb);
                         tmem_wait_ld();
                     }
-                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 1);
                     if (h == 1) {
                         tc_fence_before();
                         mbar_arrive(&bars->o_free);            // accumulator may be overwritten from here on
                         if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 2);
                     }
-                    if (warp_active) {
-                        unsigned char* half = dst + h * (kTileRows * 128);
+                    if (row_ok && !ABLATE(2)) {
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
                             const uint32_t (&r)[32] = c ? rb : ra;
 #pragma unroll
-                            for (int ch = 0; ch < 4; ++ch) {
-                                uint4 v;
-                                v.x = pack_bf16_alu(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-                                v.y = pack_bf16_alu(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-                                v.z = pack_bf16_alu(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-                                v.w = pack_bf16_alu(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-                                *reinterpret_cast<uint4*>(half + (((c * 4 + ch) ^ (row & 7)) << 4)) = v;
+                            for (int v8 = 0; v8 < 2; ++v8) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    w[e] = pack_bf16_alu(__uint_as_float(r[v8 * 16 + 2 * e]), __uint_as_float(r[v8 * 16 + 2 * e + 1]));
+                                st_global_v8(out_row + h * 64 + c * 32 + v8 * 16, w);
                             }
                         }
                     }
-                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 2);
-                    fence_async_smem();
-                    mbar_arrive(&bars->stg_full[which][h]);
-                    if (which == 0 && quad == 0 && lane == 0) TRACE(4 + h, g, 3);
                 }
                 if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 3);
             }
-        }
-    } else {
-        // ------------------------------------------------------------------ TMA store issuers (warps 2, 3)
-        const int which = warp - 2;
-        if (lane == 0) {
-            const CUtensorMap* const tmap = which ? &ty : &tal;
-            unsigned char* const stg = stg_s + which * kQBytes;
-            int g = 0;
-            bool ok = true;
-            for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
-                const RUnit un = decode_unit(rp, u);
-                const int g_first = un.tile * rp.groups_per_tile;
-                const int ng = min(rp.groups_per_tile, p.na - g_first);
-                for (int i = 0; ok && i < un.n_it; ++i, ++g) {
-                    const int key = (un.f_begin + i) * b1 + un.k;
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        if (!mbar_wait(&bars->stg_full[which][h], g & 1)) { fail(51); ok = false; break; }
-                        for (int gi = 0; gi < ng; ++gi) {
-                            const int aj0 = (un.bhl * p.na + g_first + gi) * b2;
-                            tma_store_3d(tmap, stg + h * (kTileRows * 128) + gi * RG * 128, h * 64, key, aj0);
-                        }
-                        tma_store_commit();
-                        // all groups but the newest have been read: the other slot may be refilled
-                        tma_store_wait_read<1>();
-                        if (g > 0 || h == 1) mbar_arrive(&bars->stg_free[which][h ^ 1]);
-                    }
-                }
-            }
-            tma_store_wait_all<0>();
         }
     }
 
@@ -439,7 +412,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 
 #ifdef SFM_TRACE
 long long* g_sfm_trace = nullptr;
+int g_sfm_ablate = 0;
 extern "C" void sfm_debug_set_trace(long long* p) { g_sfm_trace = p; }
+extern "C" void sfm_debug_set_ablate(int a) { g_sfm_ablate = a; }
 #endif
 
 // Launches the tensor-core row step for one chunk as a persistent grid.  `status` is a device int the
@@ -456,6 +431,7 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q,k,v,aL
     rp.status = status;
 #ifdef SFM_TRACE
     rp.trace = g_sfm_trace;
+    rp.ablate = g_sfm_ablate;
 #endif
     dim3 grid(rp.n_units < num_sms ? rp.n_units : num_sms);
     auto go = [&](auto kernel) -> int {
