@@ -66,7 +66,7 @@ int make_plan(Plan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int 
     pl->off_status = off; off = align256(off + sizeof(int));
     pl->off_aL = off; off = align256(off + aj * pl->n_keys * kHeadDim * 2);
     pl->off_Y = off;  off = align256(off + aj * pl->n_keys * kHeadDim * 2);
-    pl->off_cL = off; off = align256(off + aj * pl->n_keys * 4);
+    pl->off_cL = off; off = align256(off + aj * (size_t)((pl->n_keys + 3) & ~3) * 4);
     pl->off_lse = pl->off_aR = pl->off_cR = off;
     if (num_iters > 1) {
         pl->off_lse = off; off = align256(off + aj * blk.b1 * 4);
@@ -102,6 +102,7 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     p.aR = (__nv_bfloat16*)(base + pl.off_aR);
     p.cR = (float*)(base + pl.off_cR);
     p.H = H; p.n_q = n_q; p.A = pl.A; p.F = pl.F; p.n_keys = pl.n_keys;
+    p.n_keys_c = (pl.n_keys + 3) & ~3;
     p.na_cta = pl.na_cta;
     p.causal_groups = causal_groups;
     p.scale = sm_scale;
@@ -116,11 +117,15 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
     int* status = reinterpret_cast<int*>(base + pl.off_status);
-    CUtensorMap maps[5];
+    CUtensorMap maps[6];
     const int rows_per_group = (pl.blk.b2 + 7) & ~7;
     const int n_s = (pl.blk.b2 + 15) & ~15;
     if (use_tc) {
         cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
+        // cL rows are padded to 16 bytes; the pad floats travel with the column step's bulk copies and
+        // must act as "key masked": fill the buffer with a huge positive bias (0x7f7f7f7f = 3.4e38).
+        e = cudaMemsetAsync(p.cL, 0x7f, (size_t)pl.nbh_chunk * pl.na_chunk * pl.blk.b2 * p.n_keys_c * sizeof(float), stream);
         if (e != cudaSuccess) return (int)e;
         const uint64_t row = (uint64_t)kHeadDim * 2, tok = (uint64_t)H * row;
         uint64_t dq[4] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)n_q, (uint64_t)B};
@@ -138,6 +143,12 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
         if ((rc = make_tmap_bf16(&maps[2], vc, 4, dk, sk, bk))) return rc;
         if ((rc = make_tmap_bf16(&maps[3], p.aL, 3, db, sb, bb))) return rc;
         if ((rc = make_tmap_bf16(&maps[4], p.Y, 3, db, sb, bb))) return rc;
+        // queries of one (query group, column): rows of the token grid at a fixed column
+        const int rows_per_quadrant = (pl.blk.b1 + 3) / 4;
+        uint64_t dqr[5] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)w, (uint64_t)(n_q / w), (uint64_t)B};
+        uint64_t sqr[4] = {row, tok, (uint64_t)w * tok, (uint64_t)q_bs * 2};
+        uint32_t bqr[5] = {64, 1, 1, (uint32_t)rows_per_quadrant, 1};
+        if ((rc = make_tmap_bf16(&maps[5], q, 5, dqr, sqr, bqr))) return rc;
     }
 
     const int BH = B * H;

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kLWarps * 32, 1) monarch_l_kernel(MonarchParam
 
     const __nv_bfloat16* a_src = p.aL + aj * p.n_keys * kHeadDim;
     const __nv_bfloat16* y_src = kLseOnly ? nullptr : p.Y + aj * p.n_keys * kHeadDim;
-    const float* c_src = p.cL + aj * p.n_keys;
+    const float* c_src = p.cL + aj * p.n_keys_c;
 
     {   // queries Q[a, i0.., j]: rows of 256 bytes gathered from natural order
         const __nv_bfloat16* qb = p.q + (long long)b * p.q_bs + (long long)hd * kHeadDim;
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(128, 2) monarch_l_iter_kernel(MonarchParams p)
     const int kr[2] = {key0 + warp * 16 + g, key0 + warp * 16 + g + 8};
     float cl[2];
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) cl[hh] = kr[hh] < nkeys ? p.cL[aj * nkeys + kr[hh]] : INFINITY;
+    for (int hh = 0; hh < 2; ++hh) cl[hh] = kr[hh] < nkeys ? p.cL[aj * p.n_keys_c + kr[hh]] : INFINITY;
 
     float o[kHeadDim / 8][4];
 #pragma unroll

@@ -11,8 +11,8 @@
 // writes the unit's output rows to natural token order with 32-byte stores.
 //
 // The 128-row MMA tile is much taller than b1 (30 at 480p framewise), so query row i is placed on
-// tile row (i mod 4)*32 + i/4: the four warps of a warpgroup (one per TMEM lane quadrant) then
-// share the softmax work.  The other tile rows hold stale data and are never read back.
+// tile row (i / R4)*32 + i % R4 with R4 = ceil(b1/4): the four warps of a warpgroup (one per TMEM
+// lane quadrant) then share the softmax work.  The other tile rows hold stale data and are never read back.
 //
 // Warp roles (16 warps): 0 = producer (TMA tiles, bias slices, query gather), 1 = PV-GEMM issuer (owns the
 // TMEM allocation), 2 = S-GEMM issuer, 3 idle, 4..7 / 8..11 = softmax warpgroups (even / odd tiles),
@@ -42,6 +42,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units: accumulators are resca
 struct LTcParams {
     MonarchParams mp;
     int n_units;     // nbh * na * b2
+    int q_rows_tma;  // the b1 query rows of a unit are consecutive rows of the token grid: load them with TMA
     int* status;
 };
 
@@ -55,7 +56,7 @@ struct __align__(8) Barriers {
     uint32_t tmem_base;
     volatile int abort_flag;
     float stats[2][2][128];                // [warpgroup][m | l][tile row]
-    float cl[kYStages][kKT];               // bias slices travelling with the Y ring
+    alignas(16) float cl[kYStages][kKT];   // bias slices (log2 units) travelling with the Y ring
 };
 
 constexpr int kQBytes = 2 * 128 * 128;     // query tile, two 64-column halves
@@ -77,7 +78,8 @@ __device__ __forceinline__ LUnit decode_unit(const MonarchParams& p, int u) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_constant__ CUtensorMap ty, LTcParams lp) {
+monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_constant__ CUtensorMap ty,
+                    const __grid_constant__ CUtensorMap tqr, LTcParams lp) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
@@ -92,6 +94,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     const int n_keys = p.n_keys;
     const int n_tiles = (n_keys + kKT - 1) / kKT;
     const long long tok_pitch = (long long)p.H * kHeadDim;
+    const int R4 = (b1 + 3) >> 2;               // query rows per TMEM lane quadrant: row i sits on tile row (i/R4)*32 + i%R4
 
     if (tid == 0) {
         mbar_init(&bars->q_full, 1);
@@ -132,22 +135,35 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
             const int a_abs = p.a0 + un.al;
             const int aj = (un.bhl * p.na + un.al) * b2 + un.j;
-            // queries: row i -> tile row (i & 3) * 32 + (i >> 2), 128-byte swizzled halves
+            // queries: row i -> tile row (i / R4) * 32 + i % R4, 128-byte swizzled halves
             if (uc > 0) {
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(&bars->q_empty, (uc - 1) & 1) ? 1 : 0;
                 if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(10); break; }
             }
-            const __nv_bfloat16* qb = p.q + (long long)b * p.q_bs + (long long)hd * kHeadDim;
-            for (int idx = lane; idx < b1 * 16; idx += 32) {
-                const int i = idx >> 4, ch = idx & 15;
-                const uint4 val = *reinterpret_cast<const uint4*>(qb + (blk.row_token(a_abs, i) + un.j) * tok_pitch + ch * 8);
-                const int r = (i & 3) * 32 + (i >> 2);
-                *reinterpret_cast<uint4*>(q_s + (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = val;
+            if (lp.q_rows_tma) {
+                if (lane == 0) {
+                    const int tok0 = blk.row_token(a_abs, 0);
+                    const int frow0 = tok0 / blk.w, col = tok0 - frow0 * blk.w + un.j;
+                    const int nq = (b1 + R4 - 1) / R4;                       // quadrants that hold rows
+                    mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(nq * R4 * 256));
+                    for (int qd = 0; qd < nq; ++qd) {
+                        tma_load_5d(q_s + qd * 32 * 128, &tqr, &bars->q_full, 0, hd, col, frow0 + qd * R4, b);
+                        tma_load_5d(q_s + 128 * 128 + qd * 32 * 128, &tqr, &bars->q_full, 64, hd, col, frow0 + qd * R4, b);
+                    }
+                }
+            } else {
+                const __nv_bfloat16* qb = p.q + (long long)b * p.q_bs + (long long)hd * kHeadDim;
+                for (int idx = lane; idx < b1 * 16; idx += 32) {
+                    const int i = idx >> 4, ch = idx & 15;
+                    const uint4 val = *reinterpret_cast<const uint4*>(qb + (blk.row_token(a_abs, i) + un.j) * tok_pitch + ch * 8);
+                    const int r = (i / R4) * 32 + (i % R4);
+                    *reinterpret_cast<uint4*>(q_s + (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = val;
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->q_full);
             }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->q_full);
             // key tiles: aL into its ring, then Y + the bias slice into theirs
             for (int t = 0; t < n_tiles; ++t, ++g) {
                 const int sa = g % kAStages, sy = g % kYStages;
@@ -162,16 +178,14 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 }
                 if (lane == 0 && g >= kYStages) okw = mbar_wait(&bars->y_empty[sy], ((g / kYStages) - 1) & 1) ? 1 : 0;
                 if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(12); ok = false; break; }
-                const float* csrc = p.cL + (long long)aj * n_keys + t * kKT;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = t * kKT + lane * 4 + e;
-                    bars->cl[sy][lane * 4 + e] = key < n_keys ? csrc[lane * 4 + e] * kLog2e : INFINITY;   // +inf masks the key
-                }
+                // bias slice: the part of the row that exists comes with a bulk copy, the rest masks its keys
+                const int have = min(kKT, p.n_keys_c - t * kKT);          // floats to copy (multiple of 4)
+                for (int e = have + lane; e < kKT; e += 32) bars->cl[sy][e] = INFINITY;
                 __syncwarp();
                 if (lane == 0) {
                     unsigned char* yt = y_s + sy * kTileBytes;
-                    mbar_arrive_expect_tx(&bars->y_full[sy], (uint32_t)kTileBytes);
+                    mbar_arrive_expect_tx(&bars->y_full[sy], (uint32_t)(kTileBytes + have * 4));
+                    bulk_load(bars->cl[sy], p.cL + (long long)aj * p.n_keys_c + t * kKT, (uint32_t)(have * 4), &bars->y_full[sy]);
                     tma_load_3d(yt, &ty, &bars->y_full[sy], 0, t * kKT, aj);
                     tma_load_3d(yt + kKT * 128, &ty, &bars->y_full[sy], 64, t * kKT, aj);
                 }
@@ -262,7 +276,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     tmem_ld32(s_t + c0, r);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaf(__uint_as_float(r[c]), scale_l2, -cs[c0 + c]));
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaf(__uint_as_float(r[c]), scale_l2, -kLog2e * cs[c0 + c]));
                 }
                 // lazy rescale: keep the old reference while the maximum grew by less than the threshold
                 bool rescale = false;
@@ -301,8 +315,8 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     uint32_t pk[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        float e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, -cs[c0 + c]) + neg_m);
-                        float e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, -cs[c0 + c + 1]) + neg_m);
+                        float e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, fmaf(-kLog2e, cs[c0 + c], neg_m)));
+                        float e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, fmaf(-kLog2e, cs[c0 + c + 1], neg_m)));
                         lsum += e0 + e1;
                         pk[c >> 1] = pack_bf16_alu(e0, e1);
                     }
@@ -326,7 +340,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         // ------------------------------------------------------------------ epilogue warpgroup
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        const int i_row = lane * 4 + quad;
+        const int i_row = lane < R4 ? quad * R4 + lane : b1;   // query index held by this tile row (b1 = none)
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
         int uc = 0;
         bool ok = true;
@@ -388,16 +402,18 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
 
 // Launches the tensor-core column step for one chunk as a persistent grid.  maps = {aL, Y} with a
 // (64, 128 keys, 1) box.
-int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps, int* status, int num_sms, cudaStream_t s) {
+int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q rows */, int* status, int num_sms,
+                     cudaStream_t s) {
     LaunchScope scope(kClsLStep, s);
     LTcParams lp;
     lp.mp = p;
     lp.n_units = p.nbh * p.na * p.blk.b2;
     lp.status = status;
+    lp.q_rows_tma = (p.blk.f_tied == 1 || p.blk.h_reduce == 1) ? 1 : 0;
     dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
     cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    monarch_l_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], lp);
+    monarch_l_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
     return (int)cudaGetLastError();
 }
 

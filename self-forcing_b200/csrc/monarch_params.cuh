@@ -8,7 +8,7 @@ namespace sfm {
 // The row step writes its results for the chunk into the bridge; the column step consumes them.
 //
 // Bridge layout (chunk-local), with aj = (bh_local*na + a_local)*b2 + j and key = f*b1 + k:
-//   aL, Y : bf16 [aj][n_keys][128]      cL : fp32 [aj][n_keys]
+//   aL, Y : bf16 [aj][n_keys][128]      cL : fp32 [aj][n_keys_c] (pitch rounded up to 16 bytes)
 // Iteration state (chunk-local too, only when num_iters > 1):
 //   aR : bf16 [bh_local][F][b1][na][b2][128]   cR : fp32 [bh_local][F][b1][na][b2]
 struct MonarchParams {
@@ -27,6 +27,7 @@ struct MonarchParams {
     int use_aR;                    // row step: take the query operand from aR/cR instead of q
     int write_Y;                   // row step: also produce Y
     int H, n_q, A, F, n_keys;      // A query groups, F cached groups, n_keys = F*b1
+    int n_keys_c;                  // row pitch of cL in floats: n_keys rounded up to a multiple of 4
     int bh0, nbh, a0, na, na_cta;  // chunk and per-CTA stacking of query groups
     int fsplit, f_per;             // row step: split of the F loop over CTAs
     int causal_groups;             // 0: none; else groups per causal block (no-cache path)

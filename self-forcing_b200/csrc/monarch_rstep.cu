@@ -210,8 +210,8 @@ __global__ void __launch_bounds__(kRWarps * 32, 1) monarch_r_kernel(MonarchParam
                 aj_row[hh] = ((long long)bhl * p.na + a_first) * b2 + r;
             }
             if (t == 0) {
-                if (row_ok[0]) p.cL[aj_row[0] * p.n_keys + key] = cl[0];
-                if (row_ok[1]) p.cL[aj_row[1] * p.n_keys + key] = cl[1];
+                if (row_ok[0]) p.cL[aj_row[0] * p.n_keys_c + key] = cl[0];
+                if (row_ok[1]) p.cL[aj_row[1] * p.n_keys_c + key] = cl[1];
             }
 
             // ---- aL = P K, then Y = P V; normalise, stage through shared, 16-byte stores --

@@ -334,7 +334,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     if (lane == 0 && quad == 0) TRACE(6, g, 2);
                     if (row_ok) {
                         const int key = (un.f_begin + i) * b1 + un.k;
-                        p.cL[aj * p.n_keys + key] = 0.6931471805599453f * ent * inv_z - __logf(z);
+                        p.cL[aj * p.n_keys_c + key] = 0.6931471805599453f * ent * inv_z - __logf(z);
                     }
                 }
                 tc_fence_before();
