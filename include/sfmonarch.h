@@ -32,6 +32,7 @@ extern "C" {
 #define SFM_ERR_WORKSPACE        -5   /* workspace too small                             */
 #define SFM_ERR_NO_DEVICE        -6   /* not an sm_100 device                            */
 #define SFM_ERR_DEVICE_STATUS    -7   /* a kernel recorded an internal error status      */
+#define SFM_ERR_STATIC_SCRATCH   -8   /* too large for the built-in scratch array        */
 
 /* Version of this ABI (major*100 + minor). */
 int sfm_version(void);
@@ -126,6 +127,35 @@ int sfm_monarch_fwd(const void* q, int64_t q_batch_stride,
                     int B, int H, int D, int n_q, int n_kv,
                     int f_tied, int h_reduce, int w_reduce, int h, int w,
                     float sm_scale, int num_iters, size_t bridge_budget_bytes, void* stream);
+
+/*
+ * sfm_monarch_fwd for callers that cannot give the library a workspace because they are not
+ * allowed to allocate device memory at the point of the call: code running inside another
+ * framework's memory plan, inside a region where the allocator is frozen, or in a process whose
+ * device memory is fully handed out in advance.  It has no counterpart in the reference (whose
+ * op allocates its scratch with torch.empty on every call).
+ *
+ * The scratch is an array of sfm_static_scratch_bytes() bytes (32 MiB) compiled into the
+ * library; every GPU context that loads the library carries it until the process exits.  The
+ * work is cut into chunks whose row-step results fit the array; a problem in which even one
+ * (batch*head, query group) slice does not fit is refused with SFM_ERR_STATIC_SCRATCH and
+ * nothing is launched.  At 480p every single-pass (num_iters = 1) Wan shape fits.
+ *
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside any stream capture.  No call allocates or frees memory.  All
+ * calls on a device share the one array and it keeps the previous call's contents (what must
+ * start clean is cleared on the stream first), so two calls whose kernels may overlap on the
+ * GPU (different streams without ordering between them) race: order them.
+ * Arguments and result are those of sfm_monarch_fwd.
+ */
+int sfm_monarch_fwd_static(const void* q, int64_t q_batch_stride,
+                           const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
+                           void* out, int B, int H, int D, int n_q, int n_kv,
+                           int f_tied, int h_reduce, int w_reduce, int h, int w,
+                           float sm_scale, int num_iters, void* stream);
+
+/* Size in bytes of the scratch array behind sfm_monarch_fwd_static. */
+size_t sfm_static_scratch_bytes(void);
 
 /*
  * Waits for the work queued on `stream` and reports whether any kernel of the last

@@ -27,6 +27,9 @@ SIGNATURES = {
                                 [C.c_float, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "sfm_dense_fwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p] +
                       [C.c_int] * 5 + [C.c_float, C.c_void_p]),
+    "sfm_monarch_fwd_static": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p] +
+                               [C.c_int] * 10 + [C.c_float, C.c_int, C.c_void_p]),
+    "sfm_static_scratch_bytes": (C.c_size_t, []),
     "sfm_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sfm_launch_count": (C.c_longlong, []),
     "sfm_profile_enable": (C.c_int, [C.c_int]),
@@ -61,6 +64,6 @@ def check(rc: int, what: str) -> None:
     if rc == 0:
         return
     msg = load().sfm_error_string(rc).decode()
-    if rc in (-1, -2, -3, -4, -5):
+    if rc in (-1, -2, -3, -4, -5, -8):
         raise ValueError(f"{what}: {msg} (code {rc})")
     raise SfmError(f"{what}: {msg} (code {rc})")

@@ -217,6 +217,9 @@ extern "C" const char* sfm_error_string(int code) {
         case SFM_ERR_WORKSPACE: return "workspace too small";
         case SFM_ERR_NO_DEVICE: return "no sm_100 device";
         case SFM_ERR_DEVICE_STATUS: return "kernel recorded an internal error status";
+        case SFM_ERR_STATIC_SCRATCH:
+            return "problem too large for the library's built-in scratch array: one (batch*head, query group) slice of "
+                   "row-step results must fit 32 MiB; use sfm_monarch_fwd with a caller-provided workspace";
         default: break;
     }
     if (code > 0) return cudaGetErrorString((cudaError_t)code);
@@ -237,6 +240,45 @@ extern "C" int sfm_monarch_fwd(const void* q, int64_t q_batch_stride, const void
     return run_monarch(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, out, workspace, workspace_bytes, B, H,
                        D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters, 0, bridge_budget_bytes,
                        (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward pass on library-owned scratch, for callers that must not allocate.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = 32ull << 20;
+// Lives in every CUDA context that loads this library, for the life of the process.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" size_t sfm_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int sfm_monarch_fwd_static(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                                      int64_t cache_batch_stride, void* out, int B, int H, int D, int n_q, int n_kv,
+                                      int f_tied, int h_reduce, int w_reduce, int h, int w, float sm_scale,
+                                      int num_iters, void* stream) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return SFM_ERR_UNSUPPORTED;
+    if (!g_static_scratch_ptr[dev]) {
+        // The array's name is only a host-side handle; kernels need its address on the current device.
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    // Cut the work so that one chunk of row-step results fits the array; refuse what cannot fit.
+    const size_t budget = kStaticScratchBytes - (64u << 10);
+    Plan pl;
+    int rc = make_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters, budget);
+    if (rc) return rc;
+    if (pl.total > kStaticScratchBytes) return SFM_ERR_STATIC_SCRATCH;
+    return run_monarch(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, out, g_static_scratch_ptr[dev],
+                       kStaticScratchBytes, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters, 0,
+                       budget, (cudaStream_t)stream);
 }
 
 extern "C" int sfm_monarch_nocache_fwd(const void* q, const void* k, const void* v, void* k_mon, void* v_mon,
