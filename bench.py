@@ -42,6 +42,12 @@ CHUNK = CHUNK_FRAMES * H_GRID * W_GRID          # 4680 tokens
 N_LAYER_CACHES = 4                              # rotated so K/V (201 MB per layer at k=7) is never L2 resident
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each kernel at the bench
+# workload, from the ncu capture summarised in profiles/monarch_framewise_k7_ncu.md.
+NCU_TRAFFIC = {("framewise", 7): {"monarch_row_step": 257.7e6 + 566.2e6, "monarch_col_step": 623.5e6 + 15.6e6,
+                                  "layout_rope_cache_write": 43.2e6 + 4.6e6}}
+
+
 def algorithmic(blocking: str, k: int, heads: int = HEADS, batch: int = 1):
     """Algorithmic FLOPs and HBM bytes of one call (T = 1)."""
     n_q, n_kv = CHUNK, CHUNK * k
@@ -327,8 +333,9 @@ def main():
         dom_ms = kernels[dom]["ms_per_step"]
         dom_flops = {"monarch_row_step": r_flops, "monarch_col_step": l_flops, "dense": flops}.get(dom, 0.0)
         ach = dom_flops / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+        traffic = NCU_TRAFFIC.get((args.blocking, args.k), {}).get(dom)
         roofline = {"kernel": dom, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
-                    "frac": ach / tf_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "frac": ach / tf_peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
                     "launch_ms_per_step": dom_ms,
                     "whole_op": {"algorithmic_gflop": flops / 1e9, "algorithmic_mb": bytes_ / 1e6,
                                  "tensor_tflops": flops / (ms_step * 1e-3) / 1e12,
