@@ -18,7 +18,12 @@
 // TMEM allocation), 2 = S-GEMM issuer, 3 idle, 4..7 / 8..11 = softmax warpgroups (even / odd tiles),
 // 12..15 = epilogue warpgroup.  Every wait is bounded; a timeout records a status code.
 //
-// Arithmetic follows monarch_attn_ref_op (wan/modules/monarch_attn.py:1821-1829).
+// The same kernel, instantiated with kDense = true, is the dense attention of the dense-init chunk and
+// of the "regular" configuration: a unit is then 128 consecutive queries of one (batch, head), the
+// key / value tiles come straight from the KV cache, there is no bias and every tile row is a query.
+//
+// Arithmetic follows monarch_attn_ref_op (wan/modules/monarch_attn.py:1821-1829) and, for the dense
+// instantiation, softmax(q k^T * scale) v (wan/modules/attention.py:177-187).
 #include "monarch_params.cuh"
 #include "profile.cuh"
 #include "tc05.cuh"
@@ -41,8 +46,10 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units: accumulators are resca
 
 struct LTcParams {
     MonarchParams mp;
-    int n_units;     // nbh * na * b2
+    int n_units;     // column step: nbh * na * b2;  dense: B*H * ceil(n_q / 128)
     int q_rows_tma;  // the b1 query rows of a unit are consecutive rows of the token grid: load them with TMA
+    int n_kv;        // dense: keys per (batch, head)
+    int q_tiles;     // dense: ceil(n_q / 128)
     int* status;
 };
 
@@ -77,6 +84,9 @@ __device__ __forceinline__ LUnit decode_unit(const MonarchParams& p, int u) {
     return r;
 }
 
+// Column step: tal / ty = bridge aL / Y maps (box 64 x 128 keys x 1), tqr = query rows (5-D).
+// Dense:       tal / ty = K / V cache maps (4-D, box 64 x 1 x 128 tokens x 1), tqr = q map (same geometry).
+template <bool kDense>
 __global__ void __launch_bounds__(kThreads, 1)
 monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_constant__ CUtensorMap ty,
                     const __grid_constant__ CUtensorMap tqr, LTcParams lp) {
@@ -91,7 +101,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     const Blocking& blk = p.blk;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b1 = blk.b1, b2 = blk.b2;
-    const int n_keys = p.n_keys;
+    const int n_keys = kDense ? lp.n_kv : p.n_keys;
     const int n_tiles = (n_keys + kKT - 1) / kKT;
     const long long tok_pitch = (long long)p.H * kHeadDim;
     const int R4 = (b1 + 3) >> 2;               // query rows per TMEM lane quadrant: row i sits on tile row (i/R4)*32 + i%R4
@@ -131,20 +141,34 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         int g = 0, uc = 0;
         bool ok = true;
         for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
-            const LUnit un = decode_unit(p, u);
-            const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
-            const int a_abs = p.a0 + un.al;
-            const int aj = (un.bhl * p.na + un.al) * b2 + un.j;
-            // queries: row i -> tile row (i / R4) * 32 + i % R4, 128-byte swizzled halves
+            int bh, a_abs = 0, aj = 0, col_j = 0, qt = 0;
+            if (kDense) {
+                qt = u % lp.q_tiles;
+                bh = u / lp.q_tiles;
+            } else {
+                const LUnit un = decode_unit(p, u);
+                bh = p.bh0 + un.bhl;
+                a_abs = p.a0 + un.al;
+                aj = (un.bhl * p.na + un.al) * b2 + un.j;
+                col_j = un.j;
+            }
+            const int b = bh / p.H, hd = bh - b * p.H;
             if (uc > 0) {
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(&bars->q_empty, (uc - 1) & 1) ? 1 : 0;
                 if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(10); break; }
             }
-            if (lp.q_rows_tma) {
+            if (kDense) {
+                if (lane == 0) {                                               // 128 consecutive queries
+                    mbar_arrive_expect_tx(&bars->q_full, (uint32_t)kQBytes);
+                    tma_load_4d(q_s, &tqr, &bars->q_full, 0, hd, qt * 128, b);
+                    tma_load_4d(q_s + 128 * 128, &tqr, &bars->q_full, 64, hd, qt * 128, b);
+                }
+            } else if (lp.q_rows_tma) {
+                // queries: row i -> tile row (i / R4) * 32 + i % R4, 128-byte swizzled halves
                 if (lane == 0) {
                     const int tok0 = blk.row_token(a_abs, 0);
-                    const int frow0 = tok0 / blk.w, col = tok0 - frow0 * blk.w + un.j;
+                    const int frow0 = tok0 / blk.w, col = tok0 - frow0 * blk.w + col_j;
                     const int nq = (b1 + R4 - 1) / R4;                       // quadrants that hold rows
                     mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(nq * R4 * 256));
                     for (int qd = 0; qd < nq; ++qd) {
@@ -156,7 +180,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 const __nv_bfloat16* qb = p.q + (long long)b * p.q_bs + (long long)hd * kHeadDim;
                 for (int idx = lane; idx < b1 * 16; idx += 32) {
                     const int i = idx >> 4, ch = idx & 15;
-                    const uint4 val = *reinterpret_cast<const uint4*>(qb + (blk.row_token(a_abs, i) + un.j) * tok_pitch + ch * 8);
+                    const uint4 val = *reinterpret_cast<const uint4*>(qb + (blk.row_token(a_abs, i) + col_j) * tok_pitch + ch * 8);
                     const int r = (i / R4) * 32 + (i % R4);
                     *reinterpret_cast<uint4*>(q_s + (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = val;
                 }
@@ -164,7 +188,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->q_full);
             }
-            // key tiles: aL into its ring, then Y + the bias slice into theirs
+            // key tiles: keys into their ring, then values (+ the bias slice) into theirs
             for (int t = 0; t < n_tiles; ++t, ++g) {
                 const int sa = g % kAStages, sy = g % kYStages;
                 int okw = 1;
@@ -173,21 +197,34 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 if (lane == 0) {
                     unsigned char* at = a_s + sa * kTileBytes;
                     mbar_arrive_expect_tx(&bars->a_full[sa], (uint32_t)kTileBytes);
-                    tma_load_3d(at, &tal, &bars->a_full[sa], 0, t * kKT, aj);
-                    tma_load_3d(at + kKT * 128, &tal, &bars->a_full[sa], 64, t * kKT, aj);
+                    if (kDense) {
+                        tma_load_4d(at, &tal, &bars->a_full[sa], 0, hd, t * kKT, b);
+                        tma_load_4d(at + kKT * 128, &tal, &bars->a_full[sa], 64, hd, t * kKT, b);
+                    } else {
+                        tma_load_3d(at, &tal, &bars->a_full[sa], 0, t * kKT, aj);
+                        tma_load_3d(at + kKT * 128, &tal, &bars->a_full[sa], 64, t * kKT, aj);
+                    }
                 }
                 if (lane == 0 && g >= kYStages) okw = mbar_wait(&bars->y_empty[sy], ((g / kYStages) - 1) & 1) ? 1 : 0;
                 if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(12); ok = false; break; }
-                // bias slice: the part of the row that exists comes with a bulk copy, the rest masks its keys
-                const int have = min(kKT, p.n_keys_c - t * kKT);          // floats to copy (multiple of 4)
-                for (int e = have + lane; e < kKT; e += 32) bars->cl[sy][e] = INFINITY;
-                __syncwarp();
+                int have = 0;
+                if (!kDense) {
+                    // bias slice: the part of the row that exists comes with a bulk copy, the rest masks its keys
+                    have = min(kKT, p.n_keys_c - t * kKT);               // floats to copy (multiple of 4)
+                    for (int e = have + lane; e < kKT; e += 32) bars->cl[sy][e] = INFINITY;
+                    __syncwarp();
+                }
                 if (lane == 0) {
                     unsigned char* yt = y_s + sy * kTileBytes;
                     mbar_arrive_expect_tx(&bars->y_full[sy], (uint32_t)(kTileBytes + have * 4));
-                    bulk_load(bars->cl[sy], p.cL + (long long)aj * p.n_keys_c + t * kKT, (uint32_t)(have * 4), &bars->y_full[sy]);
-                    tma_load_3d(yt, &ty, &bars->y_full[sy], 0, t * kKT, aj);
-                    tma_load_3d(yt + kKT * 128, &ty, &bars->y_full[sy], 64, t * kKT, aj);
+                    if (kDense) {
+                        tma_load_4d(yt, &ty, &bars->y_full[sy], 0, hd, t * kKT, b);
+                        tma_load_4d(yt + kKT * 128, &ty, &bars->y_full[sy], 64, hd, t * kKT, b);
+                    } else {
+                        bulk_load(bars->cl[sy], p.cL + (long long)aj * p.n_keys_c + t * kKT, (uint32_t)(have * 4), &bars->y_full[sy]);
+                        tma_load_3d(yt, &ty, &bars->y_full[sy], 0, t * kKT, aj);
+                        tma_load_3d(yt + kKT * 128, &ty, &bars->y_full[sy], 64, t * kKT, aj);
+                    }
                 }
             }
         }
@@ -265,6 +302,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 if ((t & 1) != w) continue;
                 const int sy = g % kYStages;
                 const float* cs = bars->cl[sy];
+                const int valid = min(kKT, n_keys - t * kKT);                 // keys of this tile that exist
                 if (!mbar_wait(&bars->s_full[w], idx & 1)) { fail(31); ok = false; break; }
                 if (!mbar_wait(&bars->y_full[sy], (g / kYStages) & 1)) { fail(33); ok = false; break; }   // bias slice visible
                 tc_fence_after();
@@ -276,7 +314,12 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     tmem_ld32(s_t + c0, r);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaf(__uint_as_float(r[c]), scale_l2, -kLog2e * cs[c0 + c]));
+                    for (int c = 0; c < 32; ++c) {
+                        float x = kDense ? __uint_as_float(r[c]) * scale_l2
+                                         : fmaf(__uint_as_float(r[c]), scale_l2, -kLog2e * cs[c0 + c]);
+                        if (kDense && c0 + c >= valid) x = -INFINITY;        // keys past the end of the cache view
+                        mx = fmaxf(mx, x);
+                    }
                 }
                 // lazy rescale: keep the old reference while the maximum grew by less than the threshold
                 bool rescale = false;
@@ -315,8 +358,16 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     uint32_t pk[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        float e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, fmaf(-kLog2e, cs[c0 + c], neg_m)));
-                        float e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, fmaf(-kLog2e, cs[c0 + c + 1], neg_m)));
+                        float e0, e1;
+                        if (kDense) {
+                            e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, neg_m));
+                            e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, neg_m));
+                            if (c0 + c >= valid) e0 = 0.f;
+                            if (c0 + c + 1 >= valid) e1 = 0.f;
+                        } else {
+                            e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, fmaf(-kLog2e, cs[c0 + c], neg_m)));
+                            e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, fmaf(-kLog2e, cs[c0 + c + 1], neg_m)));
+                        }
                         lsum += e0 + e1;
                         pk[c >> 1] = pack_bf16_alu(e0, e1);
                     }
@@ -345,8 +396,11 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         int uc = 0;
         bool ok = true;
         for (int u = u_first; ok && u < lp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
-            const LUnit un = decode_unit(p, u);
-            const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
+            int bh, qt = 0;
+            LUnit un = {0, 0, 0};
+            if (kDense) { qt = u % lp.q_tiles; bh = u / lp.q_tiles; }
+            else { un = decode_unit(p, u); bh = p.bh0 + un.bhl; }
+            const int b = bh / p.H, hd = bh - b * p.H;
             if (!mbar_wait(&bars->o_full, uc & 1)) { fail(41); break; }
             tc_fence_after();
             // even tiles went to warpgroup 0, odd tiles to warpgroup 1
@@ -358,12 +412,12 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             const float w0 = has0 ? exp2f(m0 - ms) : 0.f;
             const float w1 = has1 ? exp2f(m1 - ms) : 0.f;
             const float inv = 1.0f / (w0 * l0 + w1 * l1);
-            const bool row_ok = i_row < b1;
+            bool row_ok;
+            long long tok;
+            if (kDense) { tok = (long long)qt * 128 + row; row_ok = tok < p.n_q; }
+            else { row_ok = i_row < b1; tok = row_ok ? blk.row_token(p.a0 + un.al, i_row) + un.j : 0; }
             __nv_bfloat16* out_row = nullptr;
-            if (row_ok) {
-                const long long tok = blk.row_token(p.a0 + un.al, i_row) + un.j;
-                out_row = p.out + (((long long)b * p.n_q + tok) * p.H + hd) * kHeadDim;
-            }
+            if (row_ok) out_row = p.out + (((long long)b * p.n_q + tok) * p.H + hd) * kHeadDim;
 #pragma unroll 1
             for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
                 uint32_t ra[32], rb[32];
@@ -401,7 +455,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
 }  // namespace
 
 // Launches the tensor-core column step for one chunk as a persistent grid.  maps = {aL, Y} with a
-// (64, 128 keys, 1) box.
+// (64, 128 keys, 1) box and the 5-D query-row map.
 int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q rows */, int* status, int num_sms,
                      cudaStream_t s) {
     LaunchScope scope(kClsLStep, s);
@@ -410,10 +464,36 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
     lp.n_units = p.nbh * p.na * p.blk.b2;
     lp.status = status;
     lp.q_rows_tma = (p.blk.f_tied == 1 || p.blk.h_reduce == 1) ? 1 : 0;
+    lp.n_kv = 0;
+    lp.q_tiles = 0;
     dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
-    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    monarch_l_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
+    monarch_l_tc_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
+    return (int)cudaGetLastError();
+}
+
+// Dense attention on the same kernel.  maps = {K, V, q}: 4-D (d, head, token, batch), box 64 x 1 x 128 x 1.
+int launch_dense_tc(const CUtensorMap* maps, __nv_bfloat16* out, int B, int H, int n_q, int n_kv, float scale, int* status,
+                    int num_sms, cudaStream_t s) {
+    LaunchScope scope(kClsDense, s);
+    LTcParams lp;
+    lp.mp = MonarchParams();
+    lp.mp.out = out;
+    lp.mp.H = H;
+    lp.mp.n_q = n_q;
+    lp.mp.scale = scale;
+    lp.mp.blk.b1 = 128;            // every tile row is a query
+    lp.mp.blk.b2 = 1;
+    lp.q_tiles = (n_q + 127) / 128;
+    lp.n_units = B * H * lp.q_tiles;
+    lp.n_kv = n_kv;
+    lp.q_rows_tma = 1;
+    lp.status = status;
+    dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
+    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    monarch_l_tc_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
     return (int)cudaGetLastError();
 }
 
