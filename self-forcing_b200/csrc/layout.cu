@@ -6,9 +6,11 @@
 
 namespace sfm {
 
-// One thread moves one 16-byte vector (8 bf16 = 4 rotary pairs) of one (token, head) row of q, k
-// and v.  Reads and writes are 16-byte vectors; a warp covers two full 256-byte rows per tensor.
-// The kernel is HBM bound: it reads 3 tensors and writes 3 (2 when q is absent).
+// One CTA moves one token: all heads x 16 vectors of 16 bytes (8 bf16 = 4 rotary pairs) of q, k and
+// v.  The token's position arithmetic (grid coordinates, Monarch slot) is done once per CTA and its
+// 64 (cos, sin) pairs are staged in shared memory for all heads.  Reads and writes are 16-byte
+// vectors; consecutive threads cover consecutive 256-byte rows.  The kernel is HBM bound: it reads
+// 3 tensors and writes 3 (2 when q is absent).
 __global__ void __launch_bounds__(256)
 rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k, const uint4* __restrict__ v,
                         uint4* __restrict__ q_out, uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
@@ -16,50 +18,54 @@ rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k
                         int B, int n_new, int H, int start_idx, Blocking blk, int start_frame,
                         int monarch_order, int p0, int p1) {
     constexpr int kVecPerRow = kHeadDim / 8;  // 16
-    const long long total = (long long)B * n_new * H * kVecPerRow;
+    __shared__ float2 cs_s[kHeadDim / 2];
     const int frame_tokens = blk.h * blk.w;
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        int vec = (int)(idx % kVecPerRow);
-        long long row = idx / kVecPerRow;  // (b, n, h)
-        int hd = (int)(row % H);
-        long long bn = row / H;
-        int n = (int)(bn % n_new);
-        int b = (int)(bn / n_new);
-
-        uint4 kv = k[idx];
-        uint4 vv = v[idx];
-        uint4 qv = make_uint4(0, 0, 0, 0);
-        if (q) qv = q[idx];
-
+    for (long long bn = blockIdx.x; bn < (long long)B * n_new; bn += gridDim.x) {
+        const int n = (int)(bn % n_new);
+        const int b = (int)(bn / n_new);
         if (rope) {
-            int fr = n / frame_tokens, rem = n - fr * frame_tokens;
-            int rw = rem / blk.w, cl = rem - rw * blk.w;
-            int pos_f = start_frame + fr;
-            uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
-            uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+            __syncthreads();                                    // previous token's table no longer in use
+            if (threadIdx.x < kHeadDim / 2) {
+                const int m = threadIdx.x;                      // rotary pair index within the head
+                const int fr = n / frame_tokens, rem = n - fr * frame_tokens;
+                const int rw = rem / blk.w, cl = rem - rw * blk.w;
+                const int pos = m < p0 ? start_frame + fr : (m < p0 + p1 ? rw : cl);
+                cs_s[m] = rope[pos * (kHeadDim / 2) + m];
+            }
+            __syncthreads();
+        }
+        const int dst_tok = start_idx + (monarch_order ? blk.nat2mon(n) : n);
+        const long long src_row = bn * H;
+        const long long dst_row = (long long)b * cache_batch_stride_vec + (long long)dst_tok * H * kVecPerRow;
+        for (int t = threadIdx.x; t < H * kVecPerRow; t += blockDim.x) {
+            const int vec = t & (kVecPerRow - 1);
+            const long long idx = src_row * kVecPerRow + t;
+            uint4 kv = k[idx];
+            uint4 vv = v[idx];
+            uint4 qv = make_uint4(0, 0, 0, 0);
+            if (q) qv = q[idx];
+            if (rope) {
+                uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
+                uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                int m = vec * 4 + p;  // rotary pair index within the head
-                int pos = m < p0 ? pos_f : (m < p0 + p1 ? rw : cl);
-                float2 cs = rope[pos * (kHeadDim / 2) + m];
-                {
-                    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&kw[p]);
-                    float re = __low2float(x), im = __high2float(x);
-                    kw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
-                }
-                if (q) {
-                    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&qw[p]);
-                    float re = __low2float(x), im = __high2float(x);
-                    qw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
+                for (int p = 0; p < 4; ++p) {
+                    const float2 cs = cs_s[vec * 4 + p];
+                    {
+                        __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&kw[p]);
+                        float re = __low2float(x), im = __high2float(x);
+                        kw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
+                    }
+                    if (q) {
+                        __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&qw[p]);
+                        float re = __low2float(x), im = __high2float(x);
+                        qw[p] = pack_bf16(re * cs.x - im * cs.y, re * cs.y + im * cs.x);
+                    }
                 }
             }
+            if (q) q_out[idx] = qv;
+            k_cache[dst_row + t] = kv;
+            v_cache[dst_row + t] = vv;
         }
-        if (q) q_out[idx] = qv;
-        int dst_tok = start_idx + (monarch_order ? blk.nat2mon(n) : n);
-        long long dst = (long long)b * cache_batch_stride_vec + ((long long)dst_tok * H + hd) * kVecPerRow + vec;
-        k_cache[dst] = kv;
-        v_cache[dst] = vv;
     }
 }
 
@@ -123,10 +129,10 @@ extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v,
     if (cache_batch_stride < (int64_t)(start_idx + n_new) * H * D && B > 1) return SFM_ERR_BAD_SHAPE;
     int c = D / 2;
     int p0 = c - 2 * (c / 3), p1 = c / 3;
-    long long total = (long long)B * n_new * H * (D / 8);
-    int threads = 256;
-    long long want = (total + threads - 1) / threads;
-    int blocks = (int)(want < 148LL * 16 ? want : 148LL * 16);  // grid-stride; 16 resident CTAs per SM
+    int threads = H * (D / 8);
+    threads = threads > 256 ? 256 : ((threads + 31) & ~31);
+    long long want = (long long)B * n_new;                       // one token per CTA pass
+    int blocks = (int)(want < 148LL * 32 ? want : 148LL * 32);  // grid-stride over tokens
     LaunchScope scope(kClsLayout, (cudaStream_t)stream);
     rope_cache_write_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
         (const uint4*)q, (const uint4*)k, (const uint4*)v, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache,
