@@ -106,7 +106,7 @@ template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setma
 
 // 32-byte store of 16 bf16 to global memory (pointer 32-byte aligned).
 __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+    asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
                  "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 
