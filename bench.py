@@ -44,7 +44,7 @@ N_LAYER_CACHES = 4                              # rotated so K/V (201 MB per lay
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each kernel at the bench
 # workload, from the ncu capture summarised in profiles/monarch_framewise_k7_ncu.md.
-NCU_TRAFFIC = {("framewise", 7): {"monarch_row_step": 257.7e6 + 566.2e6, "monarch_col_step": 623.5e6 + 15.6e6,
+NCU_TRAFFIC = {("framewise", 7): {"monarch_row_step": 262.5e6 + 565.3e6, "monarch_col_step": 624.0e6 + 13.4e6,
                                   "layout_rope_cache_write": 43.2e6 + 4.6e6}}
 
 
@@ -337,6 +337,9 @@ def main():
         roofline = {"kernel": dom, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
                     "frac": ach / tf_peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
                     "launch_ms_per_step": dom_ms,
+                    # what the kernel actually moves through HBM (bridge included), against the copy peak
+                    "dram_traffic_gbs": (traffic / (dom_ms * 1e-3) / 1e9) if traffic and dom_ms > 0 else None,
+                    "dram_traffic_frac": (traffic / (dom_ms * 1e-3) / 1e9 / hbm_peak) if traffic and dom_ms > 0 else None,
                     "whole_op": {"algorithmic_gflop": flops / 1e9, "algorithmic_mb": bytes_ / 1e6,
                                  "tensor_tflops": flops / (ms_step * 1e-3) / 1e12,
                                  "tensor_frac": flops / (ms_step * 1e-3) / 1e12 / tf_peak,

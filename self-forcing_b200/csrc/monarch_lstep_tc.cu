@@ -361,7 +361,8 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
                             const uint32_t off = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;   // same geometry for both tiles
-                            mma_ss_masked(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0, dis);
+                            if (kDense) mma_ss(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0);
+                            else mma_ss_masked(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0, dis);
                         }
                         mma_commit(&bars->a_empty[sa]);
                         if (us == 0) LTRACE(0, gt, 2);
@@ -399,9 +400,13 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                         const uint64_t yd = y_desc0 + (uint64_t)((sy * kTileBytes) >> 4);
                         const uint32_t dis = dis_mask(us);
 #pragma unroll
-                        for (int kk = 0; kk < kKT / 16; ++kk)
-                            mma_ts_masked(tmem + col_o(w), tmem + col_s(w) + kk * 8, yd + ((kk * 2048) >> 4), idesc_o,
-                                          (t >= 2) || (kk > 0), dis);
+                        for (int kk = 0; kk < kKT / 16; ++kk) {
+                            if (kDense)
+                                mma_ts(tmem + col_o(w), tmem + col_s(w) + kk * 8, yd + ((kk * 2048) >> 4), idesc_o, (t >= 2) || (kk > 0));
+                            else
+                                mma_ts_masked(tmem + col_o(w), tmem + col_s(w) + kk * 8, yd + ((kk * 2048) >> 4), idesc_o,
+                                              (t >= 2) || (kk > 0), dis);
+                        }
                         mma_commit(&bars->y_empty[sy]);
                         if (us == 0) LTRACE(1, gt, 2);
                     }
@@ -617,9 +622,10 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
     if (lp.U > SFM_L_CAPU) lp.U = SFM_L_CAPU;
 #endif
     lp.status = status;
-    // A TMA box lands on whole 8-row swizzle atoms; unit slots that start elsewhere are filled by the
-    // producer warp with plain loads.
-    lp.q_rows_tma = ((p.blk.f_tied == 1 || p.blk.h_reduce == 1) && (lp.U == 1 || lp.R4 % 8 == 0)) ? 1 : 0;
+    // Query rows that are consecutive rows of the token grid come by TMA (the 128-byte swizzle is a function
+    // of the shared-memory address, so a box may land on any 128-byte row of the tile); other blockings
+    // are gathered by the producer warp with plain loads.
+    lp.q_rows_tma = (p.blk.f_tied == 1 || p.blk.h_reduce == 1) ? 1 : 0;
     lp.n_kv = 0;
     lp.q_tiles = 0;
 #ifdef SFM_TRACE
