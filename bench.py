@@ -239,6 +239,97 @@ def workload_config(args):
             "parallelism": f"dp{args.gpus} (independent chunks per GPU, no collective)"}
 
 
+def run_ulysses(args, sfb, rank, world, device, barrier):
+    """Wan-14B self-attention layer (40 heads x 128) on one 3-frame chunk with the heads sharded over
+    the ranks: every rank holds 4680/P tokens of q, k, v outside attention and 40/P heads (with their
+    KV cache) inside it.  Strong scaling: the total work is fixed."""
+    import torch.distributed as dist
+    from self_forcing_b200.ulysses import UlyssesSelfAttention, tokens_to_heads, heads_to_tokens
+    heads = 40
+    if heads % world or CHUNK % world:
+        raise SystemExit("--ulysses needs a GPU count that divides 40 heads and 4680 tokens")
+    hp, sp = heads // world, CHUNK // world
+    k = args.k
+    n_kv = k * CHUNK
+    g = torch.Generator(device="cpu").manual_seed(200 + rank)
+    mk = lambda n, h: torch.randn(1, n, h, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16).to(device)
+    q, kn, vn = mk(sp, heads), mk(sp, heads), mk(sp, heads)
+    caches = []
+    for _ in range(2):                                   # 2 x 2 x 32760 x (40/P) x 128 x 2 B: larger than L2 up to P = 4
+        kc = torch.zeros(1, 7 * CHUNK, hp, HEAD_DIM, dtype=torch.bfloat16, device=device)
+        vc = torch.zeros_like(kc)
+        kc[:, :n_kv - CHUNK] = mk(n_kv - CHUNK, hp)
+        vc[:, :n_kv - CHUNK] = mk(n_kv - CHUNK, hp)
+        caches.append((kc, vc))
+    ft, hr, wr = BLOCKINGS[args.blocking]
+    attn = UlyssesSelfAttention((ft, hr, wr, H_GRID, W_GRID))
+    state = {"i": 0}
+    start, start_frame = n_kv - CHUNK, CHUNK_FRAMES * (k - 1)
+
+    def step():
+        kc, vc = caches[state["i"] % len(caches)]; state["i"] += 1
+        return attn(q, kn, vn, kc, vc, start, n_kv, start_frame)
+
+    if args.p2p:
+        if world == 1:
+            raise SystemExit("--p2p needs more than one GPU")
+        from self_forcing_b200.ulysses import PeerShardedSelfAttention
+        peer_attn = PeerShardedSelfAttention((ft, hr, wr, H_GRID, W_GRID), 1, CHUNK, heads, device)
+        # the projections of the real model would write their outputs here
+        peer_attn.q_in.copy_(q); peer_attn.k_in.copy_(kn); peer_attn.v_in.copy_(vn)
+        expect = step()
+        caches = [(kc.clone(), vc.clone()) for kc, vc in caches]     # same cache contents for the check
+        kc0, vc0 = caches[0]
+        got = peer_attn(kc0, vc0, start, n_kv, start_frame)
+        torch.cuda.synchronize()
+        if not torch.equal(got, expect):
+            raise SystemExit(f"rank {rank}: peer-memory path differs from the all-to-all path")
+
+        def step():
+            kc, vc = caches[state["i"] % len(caches)]; state["i"] += 1
+            return peer_attn(kc, vc, start, n_kv, start_frame)
+
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    ms_total = time_steps(step, args.steps, args.warmup, barrier)
+    clocks = sampler.stop()
+
+    # split: the two exchanges alone, and the attention alone, over the same number of steps
+    def a2a_in():
+        return tokens_to_heads([q, kn, vn])
+    qh, kh, vh = a2a_in()
+
+    def attn_only():
+        kc, vc = caches[state["i"] % len(caches)]; state["i"] += 1
+        return sfb.rope_monarch_attn_with_kv_cache(qh, kh, vh, kc[:, :n_kv], vc[:, :n_kv], start, n_kv, start_frame,
+                                                   ft, hr, wr, H_GRID, W_GRID)
+    oh = attn_only()
+
+    def a2a_out():
+        return heads_to_tokens(oh)
+    ms_in = time_steps(a2a_in, args.steps, 3, barrier)
+    ms_attn = time_steps(attn_only, args.steps, 3, barrier)
+    ms_out = time_steps(a2a_out, args.steps, 3, barrier)
+    t = torch.tensor([ms_total, ms_in, ms_attn, ms_out], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_in, ms_attn, ms_out = (x / args.steps for x in t.tolist())
+    if rank == 0:
+        flops = algorithmic(args.blocking, k, heads=heads)[0]
+        print(json.dumps({
+            "metric": "monarch_attn_latent_frames_per_s", "value": CHUNK_FRAMES / (ms_total * 1e-3),
+            "unit": "latent frames/s (one Wan-14B attention layer call per 3-frame chunk)",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"Wan-14B self-attention op, {args.blocking}, 4680-token chunk vs {n_kv}-token KV cache, "
+                                   f"40 heads x 128 sharded {hp} per GPU, tokens sharded {sp} per GPU outside attention",
+                       "parallelism": (f"ulysses{world} (kernels gather q,k,v and scatter the result over peer memory; "
+                                       "two device barriers)") if args.p2p else
+                                      f"ulysses{world} (all-to-all q,k,v in; all-to-all out; NCCL)"},
+            "split_ms": {"all_to_all_qkv": ms_in, "rope_cache_attention": ms_attn, "all_to_all_out": ms_out},
+            "algorithmic_gflop": flops / 1e9, "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -249,6 +340,11 @@ def main():
     ap.add_argument("--k", type=int, default=7)
     ap.add_argument("--sweep", default=None, help="also time every blocking x k and write a JSON table here")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ulysses", action="store_true",
+                    help="time the Wan-14B attention layer (40 heads) with heads sharded over the GPUs "
+                         "(token shards outside attention, two all-to-alls per layer) instead of the headline workload")
+    ap.add_argument("--p2p", action="store_true",
+                    help="with --ulysses: the kernels gather / scatter over peer memory instead of the two NCCL all-to-alls")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -275,6 +371,12 @@ def main():
     import self_forcing_b200 as sfb
     from self_forcing_b200 import _lib
     lib = _lib.load()
+
+    if args.ulysses:
+        run_ulysses(args, sfb, rank, world, device, barrier)
+        if use_dist:
+            dist.destroy_process_group()
+        return
 
     q, kn, vn, caches = make_inputs(args.k, 100 + rank, device)
     qd, kd, vd = q.to(device), kn.to(device), vn.to(device)

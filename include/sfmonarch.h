@@ -196,6 +196,45 @@ int sfm_dense_fwd(const void* q, int64_t q_batch_stride,
                   float sm_scale, void* stream);
 
 /*
+ * Head-sharded attention across the GPUs of one box (Ulysses style), with the exchange done by
+ * the kernels themselves over peer memory instead of two all-to-all collectives.
+ *
+ * Outside attention every GPU p of `world` (<= 8) holds a token shard: tokens
+ * [p*n/world, (p+1)*n/world) of the chunk with ALL heads, [B, n/world, H*world, D].  Inside
+ * attention GPU `rank` works on all tokens of heads [rank*H, (rank+1)*H), H heads, with a KV
+ * cache of those heads only.  The shard pointers must be valid on the calling GPU (peer access /
+ * symmetric memory); the caller orders the calls against the peers' writes and reads with its
+ * own barriers (one before the gather: the shards are complete; one after the scatter: every
+ * row has landed).
+ *
+ *   sfm_rope_cache_write_gather   sfm_rope_cache_write whose q, k, v are read from the
+ *                                 token shards q_shards[p], k_shards[p], v_shards[p]
+ *                                 (NVLink loads); outputs are local as before
+ *   sfm_monarch_fwd_scatter       sfm_monarch_fwd (num_iters = 1) whose result rows go
+ *                                 straight to out_shards[t / (n_q/world)] at heads
+ *                                 [rank*H, (rank+1)*H) (NVLink stores) instead of a local
+ *                                 [B, n_q, H, D] tensor; SFM_ERR_UNSUPPORTED for blockings
+ *                                 whose block rows exceed 128
+ * No counterpart in the reference: its causal model has no sequence / head parallel path
+ * (the only precedent is the all-to-all wrapper for the bidirectional model,
+ * wan/distributed/xdit_context_parallel.py:131-184).
+ */
+int sfm_rope_cache_write_gather(const void* const* q_shards, const void* const* k_shards,
+                                const void* const* v_shards, int world, int rank,
+                                void* q_out, void* k_cache, void* v_cache,
+                                int64_t cache_batch_stride, const float* rope,
+                                int B, int n_new, int H, int D, int start_idx,
+                                int f_tied, int h_reduce, int w_reduce, int h, int w,
+                                int start_frame, int monarch_order, void* stream);
+int sfm_monarch_fwd_scatter(const void* q, int64_t q_batch_stride,
+                            const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
+                            void* const* out_shards, int world, int rank,
+                            void* workspace, size_t workspace_bytes,
+                            int B, int H, int D, int n_q, int n_kv,
+                            int f_tied, int h_reduce, int w_reduce, int h, int w,
+                            float sm_scale, size_t bridge_budget_bytes, void* stream);
+
+/*
  * Launch accounting and optional per-kernel timing.  Kernel classes: 0 layout / RoPE /
  * cache write, 1 Monarch row step, 2 Monarch column step, 3 Monarch iteration update,
  * 4 dense attention (SFM_NUM_KERNEL_CLASSES of them).

@@ -77,10 +77,28 @@ int make_plan(Plan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int 
     return SFM_OK;
 }
 
+// Output sharded by token over the GPUs of one box (head-sharded attention); null = plain `out`.
+struct OutShards {
+    void* const* shards;
+    int world, rank;
+};
+
 int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int64_t c_bs, void* out, void* ws,
                 size_t ws_bytes, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce,
-                int h, int w, float sm_scale, int num_iters, int causal_groups, size_t budget, cudaStream_t stream) {
-    if (!q || !kc || !vc || !out || !ws) return SFM_ERR_NULL_POINTER;
+                int h, int w, float sm_scale, int num_iters, int causal_groups, size_t budget, cudaStream_t stream,
+                const OutShards* os = nullptr) {
+    if (!q || !kc || !vc || !ws) return SFM_ERR_NULL_POINTER;
+    if (!os && !out) return SFM_ERR_NULL_POINTER;
+    if (os) {
+        if (!os->shards || os->world < 1 || os->world > kMaxPeers || os->rank < 0 || os->rank >= os->world)
+            return SFM_ERR_BAD_SHAPE;
+        if (n_q % os->world) return SFM_ERR_BAD_SHAPE;
+        for (int i = 0; i < os->world; ++i) {
+            if (!os->shards[i]) return SFM_ERR_NULL_POINTER;
+            if (reinterpret_cast<uintptr_t>(os->shards[i]) & 31) return SFM_ERR_ALIGNMENT;
+        }
+        out = os->shards[os->rank];
+    }
     Plan pl;
     int rc = make_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters, budget);
     if (rc) return rc;
@@ -94,6 +112,14 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     p.q = (const __nv_bfloat16*)q; p.q_bs = q_bs;
     p.kc = (const __nv_bfloat16*)kc; p.vc = (const __nv_bfloat16*)vc; p.c_bs = c_bs;
     p.out = (__nv_bfloat16*)out;
+    for (int i = 0; i < kMaxPeers; ++i) p.out_peers[i] = nullptr;
+    if (os) {
+        for (int i = 0; i < os->world; ++i) p.out_peers[i] = (__nv_bfloat16*)os->shards[i];
+        p.out_tokens = n_q / os->world; p.out_heads = H * os->world; p.out_head0 = os->rank * H;
+    } else {
+        p.out_peers[0] = (__nv_bfloat16*)out;
+        p.out_tokens = n_q; p.out_heads = H; p.out_head0 = 0;
+    }
     unsigned char* base = (unsigned char*)ws;
     p.aL = (__nv_bfloat16*)(base + pl.off_aL);
     p.Y = (__nv_bfloat16*)(base + pl.off_Y);
@@ -111,6 +137,8 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     // Tensor-core path: single pass, no causal mask.  The iterative and block-causal variants run
     // on the mma.sync kernels.
     const bool use_tc = (num_iters == 1 && causal_groups == 0);
+    // only the tensor-core column step knows how to scatter its rows
+    if (os && os->world > 1 && !(use_tc && pl.blk.b1 <= 128)) return SFM_ERR_UNSUPPORTED;
     int num_sms = 148;
     {
         int dev = 0;
@@ -231,6 +259,17 @@ extern "C" size_t sfm_monarch_workspace_bytes(int B, int H, int D, int n_q, int 
     Plan pl;
     if (make_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters, bridge_budget_bytes)) return 0;
     return pl.total;
+}
+
+extern "C" int sfm_monarch_fwd_scatter(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                                       int64_t cache_batch_stride, void* const* out_shards, int world, int rank,
+                                       void* workspace, size_t workspace_bytes, int B, int H, int D, int n_q, int n_kv,
+                                       int f_tied, int h_reduce, int w_reduce, int h, int w, float sm_scale,
+                                       size_t bridge_budget_bytes, void* stream) {
+    OutShards os = {out_shards, world, rank};
+    return run_monarch(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, nullptr, workspace, workspace_bytes, B, H,
+                       D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, sm_scale, 1, 0, bridge_budget_bytes,
+                       (cudaStream_t)stream, &os);
 }
 
 extern "C" int sfm_monarch_fwd(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,

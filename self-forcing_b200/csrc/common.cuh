@@ -11,6 +11,7 @@ namespace sfm {
 constexpr int kHeadDim = 128;            // the only head size the kernels are built for
 constexpr int kLds = kHeadDim + 8;       // padded shared-memory row (bf16 elements): conflict-free ldmatrix
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMaxPeers = 8;             // GPUs of one box that may share a head-sharded call
 
 // Monarch blocking of an h x w token grid (see sfmonarch.h).
 struct Blocking {

@@ -11,8 +11,19 @@ namespace sfm {
 // 64 (cos, sin) pairs are staged in shared memory for all heads.  Reads and writes are 16-byte
 // vectors; consecutive threads cover consecutive 256-byte rows.  The kernel is HBM bound: it reads
 // 3 tensors and writes 3 (2 when q is absent).
+//
+// Sources may be sharded by token over up to kMaxPeers GPUs of one box (head-sharded attention): token n
+// then lives in buffer n / src_tokens, a [B, src_tokens, src_heads, 128] tensor of which this GPU takes
+// heads [head0, head0 + H).  Buffers of other GPUs are read with plain loads over NVLink.  Unsharded
+// input is the case of one buffer with src_tokens = n_new, src_heads = H, head0 = 0.
+struct PeerSrc {
+    const uint4* q[kMaxPeers];
+    const uint4* k[kMaxPeers];
+    const uint4* v[kMaxPeers];
+};
+
 __global__ void __launch_bounds__(256)
-rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k, const uint4* __restrict__ v,
+rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int src_heads, int head0,
                         uint4* __restrict__ q_out, uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
                         long long cache_batch_stride_vec, const float2* __restrict__ rope,
                         int B, int n_new, int H, int start_idx, Blocking blk, int start_frame,
@@ -25,8 +36,7 @@ rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k
         const int b = (int)(bn / n_new);
         if (rope) {
             __syncthreads();                                    // previous token's table no longer in use
-            if (threadIdx.x < kHeadDim / 2) {
-                const int m = threadIdx.x;                      // rotary pair index within the head
+            for (int m = threadIdx.x; m < kHeadDim / 2; m += blockDim.x) {   // m: rotary pair index within the head
                 const int fr = n / frame_tokens, rem = n - fr * frame_tokens;
                 const int rw = rem / blk.w, cl = rem - rw * blk.w;
                 const int pos = m < p0 ? start_frame + fr : (m < p0 + p1 ? rw : cl);
@@ -35,11 +45,16 @@ rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k
             __syncthreads();
         }
         const int dst_tok = start_idx + (monarch_order ? blk.nat2mon(n) : n);
-        const long long src_row = bn * H;
+        const int peer = n / src_tokens;
+        const uint4* __restrict__ q = src.q[peer];
+        const uint4* __restrict__ k = src.k[peer];
+        const uint4* __restrict__ v = src.v[peer];
+        const long long src_vec0 = (((long long)b * src_tokens + (n - peer * src_tokens)) * src_heads + head0) * kVecPerRow;
+        const long long out_vec0 = bn * H * kVecPerRow;
         const long long dst_row = (long long)b * cache_batch_stride_vec + (long long)dst_tok * H * kVecPerRow;
         for (int t = threadIdx.x; t < H * kVecPerRow; t += blockDim.x) {
             const int vec = t & (kVecPerRow - 1);
-            const long long idx = src_row * kVecPerRow + t;
+            const long long idx = src_vec0 + t;
             uint4 kv = k[idx];
             uint4 vv = v[idx];
             uint4 qv = make_uint4(0, 0, 0, 0);
@@ -62,7 +77,7 @@ rope_cache_write_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k
                     }
                 }
             }
-            if (q) q_out[idx] = qv;
+            if (q) q_out[out_vec0 + t] = qv;
             k_cache[dst_row + t] = kv;
             v_cache[dst_row + t] = vv;
         }
@@ -106,13 +121,13 @@ extern "C" int sfm_rope_table(float* out, int head_dim, int max_len, double thet
     return SFM_OK;
 }
 
-extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v, void* q_out, void* k_cache,
-                                    void* v_cache, int64_t cache_batch_stride, const float* rope, int B,
-                                    int n_new, int H, int D, int start_idx, int f_tied, int h_reduce,
-                                    int w_reduce, int h, int w, int start_frame, int monarch_order,
-                                    void* stream) {
-    if (!k || !v || !k_cache || !v_cache) return SFM_ERR_NULL_POINTER;
-    if (q && !q_out) return SFM_ERR_NULL_POINTER;
+namespace {
+int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int src_heads, int head0, void* q_out,
+                          void* k_cache, void* v_cache, int64_t cache_batch_stride, const float* rope, int B, int n_new,
+                          int H, int D, int start_idx, int f_tied, int h_reduce, int w_reduce, int h, int w,
+                          int start_frame, int monarch_order, void* stream) {
+    if (!k_cache || !v_cache) return SFM_ERR_NULL_POINTER;
+    if (have_q && !q_out) return SFM_ERR_NULL_POINTER;
     if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
     Blocking blk;
     int rc = make_blocking(&blk, f_tied, h_reduce, w_reduce, h, w);
@@ -124,8 +139,7 @@ extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v,
         if (start_frame < 0 || start_frame + n_new / (h * w) > 1024 || h > 1024 || w > 1024) return SFM_ERR_BAD_SHAPE;
     }
     auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
-    if (mis(q) || mis(k) || mis(v) || mis(q_out) || mis(k_cache) || mis(v_cache) || (cache_batch_stride % 8))
-        return SFM_ERR_ALIGNMENT;
+    if (mis(q_out) || mis(k_cache) || mis(v_cache) || (cache_batch_stride % 8)) return SFM_ERR_ALIGNMENT;
     if (cache_batch_stride < (int64_t)(start_idx + n_new) * H * D && B > 1) return SFM_ERR_BAD_SHAPE;
     int c = D / 2;
     int p0 = c - 2 * (c / 3), p1 = c / 3;
@@ -135,10 +149,47 @@ extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v,
     int blocks = (int)(want < 148LL * 32 ? want : 148LL * 32);  // grid-stride over tokens
     LaunchScope scope(kClsLayout, (cudaStream_t)stream);
     rope_cache_write_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
-        (const uint4*)q, (const uint4*)k, (const uint4*)v, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache,
-        cache_batch_stride / 8, (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0,
-        p1);
+        src, src_tokens, src_heads, head0, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache, cache_batch_stride / 8,
+        (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0, p1);
     return (int)cudaGetLastError();
+}
+}  // namespace
+
+extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v, void* q_out, void* k_cache,
+                                    void* v_cache, int64_t cache_batch_stride, const float* rope, int B,
+                                    int n_new, int H, int D, int start_idx, int f_tied, int h_reduce,
+                                    int w_reduce, int h, int w, int start_frame, int monarch_order,
+                                    void* stream) {
+    if (!k || !v) return SFM_ERR_NULL_POINTER;
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (mis(q) || mis(k) || mis(v)) return SFM_ERR_ALIGNMENT;
+    PeerSrc src = {};
+    src.q[0] = (const uint4*)q; src.k[0] = (const uint4*)k; src.v[0] = (const uint4*)v;
+    return rope_cache_write_impl(src, q != nullptr, n_new > 0 ? n_new : 1, H, 0, q_out, k_cache, v_cache,
+                                 cache_batch_stride, rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w,
+                                 start_frame, monarch_order, stream);
+}
+
+extern "C" int sfm_rope_cache_write_gather(const void* const* q_shards, const void* const* k_shards,
+                                           const void* const* v_shards, int world, int rank, void* q_out, void* k_cache,
+                                           void* v_cache, int64_t cache_batch_stride, const float* rope, int B,
+                                           int n_new, int H, int D, int start_idx, int f_tied, int h_reduce,
+                                           int w_reduce, int h, int w, int start_frame, int monarch_order,
+                                           void* stream) {
+    if (!q_shards || !k_shards || !v_shards) return SFM_ERR_NULL_POINTER;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return SFM_ERR_BAD_SHAPE;
+    if (n_new <= 0 || n_new % world) return SFM_ERR_BAD_SHAPE;
+    PeerSrc src = {};
+    for (int p = 0; p < world; ++p) {
+        if (!q_shards[p] || !k_shards[p] || !v_shards[p]) return SFM_ERR_NULL_POINTER;
+        if ((reinterpret_cast<uintptr_t>(q_shards[p]) | reinterpret_cast<uintptr_t>(k_shards[p]) |
+             reinterpret_cast<uintptr_t>(v_shards[p])) & 15)
+            return SFM_ERR_ALIGNMENT;
+        src.q[p] = (const uint4*)q_shards[p]; src.k[p] = (const uint4*)k_shards[p]; src.v[p] = (const uint4*)v_shards[p];
+    }
+    return rope_cache_write_impl(src, true, n_new / world, H * world, rank * H, q_out, k_cache, v_cache,
+                                 cache_batch_stride, rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w,
+                                 start_frame, monarch_order, stream);
 }
 
 namespace sfm {

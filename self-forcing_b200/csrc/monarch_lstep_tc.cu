@@ -559,7 +559,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     const LUnit un = decode_unit(p, u0 + us);
                     const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
                     const long long tok = blk.row_token(p.a0 + un.al, i_row) + un.j;
-                    out_row = p.out + (((long long)b * p.n_q + tok) * p.H + hd) * kHeadDim;
+                    out_row = p.out_row(b, tok, hd);
                 }
             }
 #pragma unroll 1

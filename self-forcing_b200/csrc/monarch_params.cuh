@@ -35,6 +35,18 @@ struct MonarchParams {
     float mult0;                   // row-step multiplier when the operand is q itself (scale, or
                                    // scale/(1+1e-6) on the first pass of the iterative path)
     Blocking blk;
+    // Where the column step puts its result.  Unsharded: one [B, n_q, H, 128] tensor (out_peers[0] = out,
+    // out_tokens = n_q, out_heads = H, out_head0 = 0).  Head-sharded call: the output is sharded by token
+    // over the GPUs of the box, shard t / out_tokens being a [B, out_tokens, out_heads, 128] tensor on that
+    // GPU, of which this GPU writes heads [out_head0, out_head0 + H) with plain stores over NVLink.
+    __nv_bfloat16* out_peers[kMaxPeers];
+    int out_tokens, out_heads, out_head0;
+
+    __device__ __forceinline__ __nv_bfloat16* out_row(int b, long long tok, int hd) const {
+        const int peer = (int)(tok / out_tokens);
+        const long long t = tok - (long long)peer * out_tokens;
+        return out_peers[peer] + (((long long)b * out_tokens + t) * out_heads + out_head0 + hd) * kHeadDim;
+    }
 };
 
 constexpr int kRWarps = 8;         // row-step CTA: 8 warps, one 16-row m-tile at a time each

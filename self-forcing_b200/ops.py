@@ -181,6 +181,54 @@ def rope_monarch_attn_with_kv_cache(q, k, v, k_cache, v_cache, start_idx, end_id
     return _monarch_fwd(q_rot, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
 
 
+def _ptr_array(ptrs):
+    arr = (C.c_void_p * len(ptrs))(*[C.c_void_p(int(p)) for p in ptrs])
+    return arr
+
+
+def rope_monarch_attn_with_kv_cache_sharded(q_shards, k_shards, v_shards, out_shards, rank, shard_shape, k_cache,
+                                            v_cache, start_idx, end_idx, start_frame, f_tied, h_reduce, w_reduce,
+                                            h, w, freqs=None, sm_scale=None):
+    """Head-sharded form of rope_monarch_attn_with_kv_cache for P GPUs of one box.
+
+    ``q_shards[p]``, ``k_shards[p]``, ``v_shards[p]``, ``out_shards[p]`` are device addresses (ints),
+    valid on THIS GPU, of GPU p's token shard ``shard_shape = (B, n/P, H_total, 128)`` (bf16,
+    contiguous); ``k_cache`` / ``v_cache`` hold this rank's ``H_total/P`` heads.  The gather of the
+    inputs and the scatter of the result are done by the kernels over peer memory; the caller
+    puts a barrier before (shards complete) and after (rows landed) the call.  Returns nothing:
+    the result is in the out shards."""
+    world = len(q_shards)
+    B, sp, h_total, D = shard_shape
+    if h_total % world:
+        raise ValueError("heads must divide evenly over the ranks")
+    H = h_total // world
+    n_q = sp * world
+    _cache_view_ok(k_cache, "k_cache")
+    _cache_view_ok(v_cache, "v_cache")
+    if end_idx - start_idx != n_q or end_idx > k_cache.shape[1] or k_cache.shape[2] != H:
+        raise ValueError("start_idx/end_idx or the cache's head count do not match the shards")
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    lib = _lib.load()
+    tab = _rope_table_from_freqs(freqs, k_cache.device)
+    q_rot = torch.empty((B, n_q, H, D), dtype=torch.bfloat16, device=k_cache.device)
+    rc = lib.sfm_rope_cache_write_gather(_ptr_array(q_shards), _ptr_array(k_shards), _ptr_array(v_shards), world,
+                                         int(rank), _ptr(q_rot), _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache),
+                                         _ptr(tab), B, n_q, H, D, int(start_idx), f_tied, h_reduce, w_reduce, h, w,
+                                         int(start_frame), 1, _stream())
+    _lib.check(rc, "sfm_rope_cache_write_gather")
+    n_kv = end_idx
+    kc, vc = k_cache[:, :n_kv], v_cache[:, :n_kv]
+    nbytes = lib.sfm_monarch_workspace_bytes(B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, 1, 0) or 256
+    ws = _workspace(k_cache.device, nbytes)
+    rc = lib.sfm_monarch_fwd_scatter(_ptr(q_rot), _batch_stride(q_rot), _ptr(kc), _ptr(vc), _batch_stride(kc),
+                                     _ptr_array(out_shards), world, int(rank), _ptr(ws), ws.numel(), B, H, D, n_q,
+                                     n_kv, f_tied, h_reduce, w_reduce, h, w, float(sm_scale), 0, _stream())
+    _lib.check(rc, "sfm_monarch_fwd_scatter")
+    if os.environ.get("SFM_CHECK_STATUS") == "1":
+        _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
+
+
 def monarch_attn(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale=None, block_causal_size=None, num_iters=1):
     """Same contract as the reference's monarch_attn (monarch_attn.py:1753-1776): no cache;
     with block_causal_size, causal over blocks of that many tokens (forward only)."""

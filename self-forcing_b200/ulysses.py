@@ -31,7 +31,7 @@ def tokens_to_heads(xs: Sequence[torch.Tensor], group: Optional[dist.ProcessGrou
     """[B, S/P, H, D] token shards -> [B, S, H/P, D] head shards, for several tensors in ONE
     all-to-all.  Rank r ends up with heads [r*H/P, (r+1)*H/P) of all S tokens (token order =
     rank order of the shards)."""
-    world = dist.get_world_size(group)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return [x.contiguous() for x in xs]
     n = len(xs)
@@ -52,7 +52,7 @@ def tokens_to_heads(xs: Sequence[torch.Tensor], group: Optional[dist.ProcessGrou
 
 def heads_to_tokens(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """[B, S, H/P, D] head shard -> [B, S/P, H, D] token shard (inverse of tokens_to_heads)."""
-    world = dist.get_world_size(group)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return x.contiguous()
     _check(x, world, 1)
@@ -95,3 +95,51 @@ class UlyssesSelfAttention:
         else:
             out = self._default_attn(qh, kh, vh, k_cache, v_cache, start_idx, end_idx, start_frame)
         return heads_to_tokens(out, self.group)
+
+
+class PeerShardedSelfAttention:
+    """Head-sharded self-attention of one layer in which the kernels do the exchange themselves.
+
+    Instead of two all-to-all collectives (and the packing copies around them), the fused RoPE +
+    cache-write kernel READS every rank's token shard of q, k, v over NVLink and the attention
+    kernel WRITES each result row straight into the token shard of the rank that owns the token.
+    The shards live in symmetric memory (``torch.distributed._symmetric_memory``) so that every rank
+    has the peers' addresses; two device-side barriers per call order the peer accesses:
+
+        write q, k, v into ``self.q_in`` / ``k_in`` / ``v_in`` (e.g. as outputs of the projections)
+        out = attn(k_cache, v_cache, start_idx, end_idx, start_frame)     # -> ``self.out`` (token shard)
+
+    ``out`` is overwritten by the next call; the caches hold the local heads only.  GPUs only (the
+    CPU tests cover the all-to-all path of UlyssesSelfAttention, which computes the same result).
+    """
+
+    def __init__(self, blocking, batch: int, chunk_tokens: int, heads_total: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.blocking = tuple(blocking)
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if chunk_tokens % self.world or heads_total % self.world:
+            raise ValueError("tokens and heads must divide evenly over the ranks")
+        self.shape = (batch, chunk_tokens // self.world, heads_total, 128)
+        n = batch * (chunk_tokens // self.world) * heads_total * 128
+        buf = symm_mem.empty(4 * n, dtype=torch.bfloat16, device=device)      # q, k, v in; out
+        self._hdl = symm_mem.rendezvous(buf, self.group)
+        self._buf = buf
+        views = [buf[i * n:(i + 1) * n].view(self.shape) for i in range(4)]
+        self.q_in, self.k_in, self.v_in, self.out = views
+        base = [int(p) for p in self._hdl.buffer_ptrs]
+        nbytes = n * 2
+        self._ptrs = [[b + i * nbytes for b in base] for i in range(4)]
+
+    def barrier(self):
+        self._hdl.barrier()
+
+    def __call__(self, k_cache, v_cache, start_idx, end_idx, start_frame=0):
+        from . import ops
+        self._hdl.barrier()                       # every rank's q_in / k_in / v_in are complete
+        ops.rope_monarch_attn_with_kv_cache_sharded(self._ptrs[0], self._ptrs[1], self._ptrs[2], self._ptrs[3],
+                                                    self.rank, self.shape, k_cache, v_cache, start_idx, end_idx,
+                                                    start_frame, *self.blocking)
+        self._hdl.barrier()                       # every rank's rows have landed in self.out
+        return self.out

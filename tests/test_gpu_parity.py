@@ -121,10 +121,12 @@ def test_rope_standalone(sfb, golden, sf):
     assert torch.equal(got[:, 105:], xb[:, 105:])
 
 
-def test_rope_fused_front_end(sfb):
-    """RoPE + layout + cache write in one kernel == separate rotation followed by the plain op."""
+@pytest.mark.parametrize("H", [1, 2, 3, 5])
+def test_rope_fused_front_end(sfb, H):
+    """RoPE + layout + cache write in one kernel == separate rotation followed by the plain op
+    (head counts on both sides of the 64-thread mark: the rotation table is staged per CTA)."""
     rng = np.random.default_rng(11)
-    B, H, D, h, w = 2, 3, 128, 6, 8
+    B, D, h, w = 2, 128, 6, 8
     n = 3 * h * w
     q, k, v = (bf(cases.randn(rng, B, n, H, D)).cuda() for _ in range(3))
     kbuf = bf(cases.randn(rng, B, 3 * n, H, D)).cuda()
@@ -308,3 +310,39 @@ def test_errors_are_loud(sfb):
         sfb.attention(torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device="cuda"),
                       torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device="cuda"),
                       torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.gpu
+def test_gather_scatter_shards_match_unsharded(sfb):
+    """Head-sharded entry points, two ranks emulated on one GPU: rank r gathers its heads from both token
+    shards and scatters its result rows into both output shards; together they must reproduce the
+    unsharded call bit for bit (heads are independent in every kernel)."""
+    import torch
+    from self_forcing_b200 import ops
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(7)
+    B, H, hh, ww, frames, world = 1, 4, 6, 8, 2, 2
+    n = frames * hh * ww
+    k_chunks = 3
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).to(dev)
+    q, k, v = mk(B, n, H, 128), mk(B, n, H, 128), mk(B, n, H, 128)
+    kc_full, vc_full = mk(B, k_chunks * n, H, 128), mk(B, k_chunks * n, H, 128)
+    start, end, start_frame = (k_chunks - 1) * n, k_chunks * n, frames * (k_chunks - 1)
+    kc_ref, vc_ref = kc_full.clone(), vc_full.clone()
+    ref = sfb.rope_monarch_attn_with_kv_cache(q, k, v, kc_ref, vc_ref, start, end, start_frame, 1, 1, 1, hh, ww)
+    sp, hp = n // world, H // world
+    q_sh = [q[:, p * sp:(p + 1) * sp].contiguous() for p in range(world)]
+    k_sh = [k[:, p * sp:(p + 1) * sp].contiguous() for p in range(world)]
+    v_sh = [v[:, p * sp:(p + 1) * sp].contiguous() for p in range(world)]
+    out_sh = [torch.zeros(B, sp, H, 128, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    for r in range(world):
+        kc = kc_full[:, :, r * hp:(r + 1) * hp].contiguous()
+        vc = vc_full[:, :, r * hp:(r + 1) * hp].contiguous()
+        ops.rope_monarch_attn_with_kv_cache_sharded([t.data_ptr() for t in q_sh], [t.data_ptr() for t in k_sh],
+                                                    [t.data_ptr() for t in v_sh], [t.data_ptr() for t in out_sh], r,
+                                                    (B, sp, H, 128), kc, vc, start, end, start_frame, 1, 1, 1, hh, ww)
+        torch.cuda.synchronize()
+        assert torch.equal(kc, kc_ref[:, :, r * hp:(r + 1) * hp])
+        assert torch.equal(vc, vc_ref[:, :, r * hp:(r + 1) * hp])
+    got = torch.cat(out_sh, dim=1)
+    assert torch.equal(got, ref)
