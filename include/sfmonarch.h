@@ -196,6 +196,22 @@ int sfm_dense_fwd(const void* q, int64_t q_batch_stride,
                   float sm_scale, void* stream);
 
 /*
+ * sfm_rope_cache_write with the full-width RMS normalisation of q and k in front, in the same
+ * pass: per token, x <- bf16(bf16(x * rsqrt(mean(x^2 over all H*D elements) + eps)) * weight),
+ * for q with norm_q_weight and for k with norm_k_weight (bf16 [H*D] each), then the rotation,
+ * the layout and the cache write as in sfm_rope_cache_write.  v is not normalised.  q is required.
+ * Replaces: norm_q / norm_k of qkv_fn (wan/modules/causal_model.py:801-807; WanRMSNorm,
+ * wan/modules/model.py:462-478) in front of causal_rope_apply and the cache write.
+ */
+int sfm_norm_rope_cache_write(const void* q, const void* k, const void* v,
+                              const void* norm_q_weight, const void* norm_k_weight, float eps,
+                              void* q_out, void* k_cache, void* v_cache,
+                              int64_t cache_batch_stride, const float* rope,
+                              int B, int n_new, int H, int D, int start_idx,
+                              int f_tied, int h_reduce, int w_reduce, int h, int w,
+                              int start_frame, int monarch_order, void* stream);
+
+/*
  * Head-sharded attention across the GPUs of one box (Ulysses style), with the exchange done by
  * the kernels themselves over peer memory instead of two all-to-all collectives.
  *

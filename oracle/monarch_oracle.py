@@ -297,6 +297,14 @@ def dense_attention(q, k, v, softmax_scale=None):
     return torch.matmul(torch.softmax(s, dim=-1), vh).transpose(1, 2).contiguous()
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """WanRMSNorm.forward (wan/modules/model.py:470-478): normalise in fp32 over the last (full model
+    width) dimension, round back to the input dtype, then multiply by the weight."""
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return y.type_as(x) * weight
+
+
 def cache_indices(current_start: int, num_new: int, global_end: int, local_end: int,
                   cache_size: int, max_attention_size: int, local_attn_size: int = -1,
                   sink_tokens: int = 0):

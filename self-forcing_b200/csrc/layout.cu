@@ -27,9 +27,12 @@ rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int
                         uint4* __restrict__ q_out, uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
                         long long cache_batch_stride_vec, const float2* __restrict__ rope,
                         int B, int n_new, int H, int start_idx, Blocking blk, int start_frame,
-                        int monarch_order, int p0, int p1) {
+                        int monarch_order, int p0, int p1,
+                        const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, float eps) {
     constexpr int kVecPerRow = kHeadDim / 8;  // 16
     __shared__ float2 cs_s[kHeadDim / 2];
+    __shared__ float red_s[2][8];
+    __shared__ float rs_s[2];                  // 1/rms of the token's q and k rows (full width)
     const int frame_tokens = blk.h * blk.w;
     for (long long bn = blockIdx.x; bn < (long long)B * n_new; bn += gridDim.x) {
         const int n = (int)(bn % n_new);
@@ -51,6 +54,44 @@ rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int
         const uint4* __restrict__ v = src.v[peer];
         const long long src_vec0 = (((long long)b * src_tokens + (n - peer * src_tokens)) * src_heads + head0) * kVecPerRow;
         const long long out_vec0 = bn * H * kVecPerRow;
+        if (wk) {
+            // RMS normalisation over the token's full width (all heads), q and k separately
+            float sq = 0.f, sk = 0.f;
+            for (int t = threadIdx.x; t < H * kVecPerRow; t += blockDim.x) {
+                const uint4 kv = k[src_vec0 + t];
+                const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&kw[p]);
+                    const float a = __low2float(x), c = __high2float(x);
+                    sk = fmaf(a, a, fmaf(c, c, sk));
+                }
+                if (q) {
+                    const uint4 qv = q[src_vec0 + t];
+                    const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&qw[p]);
+                        const float a = __low2float(x), c = __high2float(x);
+                        sq = fmaf(a, a, fmaf(c, c, sq));
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+            }
+            __syncthreads();                                    // previous token's factors no longer in use
+            if ((threadIdx.x & 31) == 0) { red_s[0][threadIdx.x >> 5] = sq; red_s[1][threadIdx.x >> 5] = sk; }
+            __syncthreads();
+            if (threadIdx.x < 2) {
+                float tot = 0.f;
+                for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red_s[threadIdx.x][i];
+                rs_s[threadIdx.x] = rsqrtf(tot / (float)(H * kHeadDim) + eps);
+            }
+            __syncthreads();
+        }
         const long long dst_row = (long long)b * cache_batch_stride_vec + (long long)dst_tok * H * kVecPerRow;
         for (int t = threadIdx.x; t < H * kVecPerRow; t += blockDim.x) {
             const int vec = t & (kVecPerRow - 1);
@@ -59,6 +100,33 @@ rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int
             uint4 vv = v[idx];
             uint4 qv = make_uint4(0, 0, 0, 0);
             if (q) qv = q[idx];
+            if (wk) {
+                // y = bf16(bf16(x * rsqrt(mean x^2 + eps)) * weight): the two roundings of the reference
+                const uint4 wkv = reinterpret_cast<const uint4*>(wk)[t];
+                const uint32_t* wkw = reinterpret_cast<const uint32_t*>(&wkv);
+                uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
+                const float rk = rs_s[1];
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&kw[p]);
+                    const __nv_bfloat162 wv = *reinterpret_cast<const __nv_bfloat162*>(&wkw[p]);
+                    const __nv_bfloat162 y = __floats2bfloat162_rn(__low2float(x) * rk, __high2float(x) * rk);
+                    kw[p] = pack_bf16(__low2float(y) * __low2float(wv), __high2float(y) * __high2float(wv));
+                }
+                if (q) {
+                    const uint4 wqv = reinterpret_cast<const uint4*>(wq)[t];
+                    const uint32_t* wqw = reinterpret_cast<const uint32_t*>(&wqv);
+                    uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+                    const float rq = rs_s[0];
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&qw[p]);
+                        const __nv_bfloat162 wv = *reinterpret_cast<const __nv_bfloat162*>(&wqw[p]);
+                        const __nv_bfloat162 y = __floats2bfloat162_rn(__low2float(x) * rq, __high2float(x) * rq);
+                        qw[p] = pack_bf16(__low2float(y) * __low2float(wv), __high2float(y) * __high2float(wv));
+                    }
+                }
+            }
             if (rope) {
                 uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
                 uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
@@ -125,8 +193,10 @@ namespace {
 int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int src_heads, int head0, void* q_out,
                           void* k_cache, void* v_cache, int64_t cache_batch_stride, const float* rope, int B, int n_new,
                           int H, int D, int start_idx, int f_tied, int h_reduce, int w_reduce, int h, int w,
-                          int start_frame, int monarch_order, void* stream) {
+                          int start_frame, int monarch_order, void* stream, const void* wq = nullptr,
+                          const void* wk = nullptr, float eps = 0.f) {
     if (!k_cache || !v_cache) return SFM_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk)) & 15) return SFM_ERR_ALIGNMENT;
     if (have_q && !q_out) return SFM_ERR_NULL_POINTER;
     if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
     Blocking blk;
@@ -150,7 +220,8 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
     LaunchScope scope(kClsLayout, (cudaStream_t)stream);
     rope_cache_write_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
         src, src_tokens, src_heads, head0, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache, cache_batch_stride / 8,
-        (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0, p1);
+        (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0, p1,
+        (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, eps);
     return (int)cudaGetLastError();
 }
 }  // namespace
@@ -168,6 +239,23 @@ extern "C" int sfm_rope_cache_write(const void* q, const void* k, const void* v,
     return rope_cache_write_impl(src, q != nullptr, n_new > 0 ? n_new : 1, H, 0, q_out, k_cache, v_cache,
                                  cache_batch_stride, rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w,
                                  start_frame, monarch_order, stream);
+}
+
+extern "C" int sfm_norm_rope_cache_write(const void* q, const void* k, const void* v, const void* norm_q_weight,
+                                         const void* norm_k_weight, float eps, void* q_out, void* k_cache,
+                                         void* v_cache, int64_t cache_batch_stride, const float* rope, int B,
+                                         int n_new, int H, int D, int start_idx, int f_tied, int h_reduce,
+                                         int w_reduce, int h, int w, int start_frame, int monarch_order,
+                                         void* stream) {
+    if (!q || !k || !v || !norm_q_weight || !norm_k_weight) return SFM_ERR_NULL_POINTER;
+    if (!(eps >= 0.f)) return SFM_ERR_BAD_SHAPE;
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (mis(q) || mis(k) || mis(v)) return SFM_ERR_ALIGNMENT;
+    PeerSrc src = {};
+    src.q[0] = (const uint4*)q; src.k[0] = (const uint4*)k; src.v[0] = (const uint4*)v;
+    return rope_cache_write_impl(src, true, n_new > 0 ? n_new : 1, H, 0, q_out, k_cache, v_cache, cache_batch_stride,
+                                 rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w, start_frame,
+                                 monarch_order, stream, norm_q_weight, norm_k_weight, eps);
 }
 
 extern "C" int sfm_rope_cache_write_gather(const void* const* q_shards, const void* const* k_shards,

@@ -155,6 +155,43 @@ def monarch_attn_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end
     return _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
 
 
+def norm_rope_cache_write(q, k, v, k_cache, v_cache, start_idx, start_frame, f_tied, h_reduce, w_reduce, h, w,
+                          freqs=None, norm_q_weight=None, norm_k_weight=None, eps=1e-6, monarch_order=True):
+    """One kernel: optional full-width RMSNorm of q and k (WanRMSNorm, model.py:462-478, as applied in
+    qkv_fn, causal_model.py:801-807), 3-axis RoPE with frame offset (causal_model.py:687-715), and the
+    in-place write of k, v into cache tokens [start_idx, start_idx + n) in Monarch order (or natural
+    order for the dense branch).  Returns the normalised, rotated q."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _require(t, name)
+    _cache_view_ok(k_cache, "k_cache")
+    _cache_view_ok(v_cache, "v_cache")
+    B, n, H, D = q.shape
+    if k.shape != q.shape or v.shape != q.shape or start_idx + n > k_cache.shape[1]:
+        raise ValueError("q, k, v shapes or the cache extent do not match")
+    tab = _rope_table_from_freqs(freqs, q.device)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q_rot = torch.empty_like(q)
+    lib = _lib.load()
+    if (norm_q_weight is None) != (norm_k_weight is None):
+        raise ValueError("give both norm weights or neither")
+    if norm_q_weight is not None:
+        wq = norm_q_weight.detach().to(device=q.device, dtype=torch.bfloat16).contiguous()
+        wk = norm_k_weight.detach().to(device=q.device, dtype=torch.bfloat16).contiguous()
+        if wq.numel() != H * D or wk.numel() != H * D:
+            raise ValueError("norm weights must have H*D elements")
+        rc = lib.sfm_norm_rope_cache_write(_ptr(q), _ptr(k), _ptr(v), _ptr(wq), _ptr(wk), float(eps), _ptr(q_rot),
+                                           _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache), _ptr(tab), B, n, H, D,
+                                           int(start_idx), f_tied, h_reduce, w_reduce, h, w, int(start_frame),
+                                           1 if monarch_order else 0, _stream())
+        _lib.check(rc, "sfm_norm_rope_cache_write")
+    else:
+        rc = lib.sfm_rope_cache_write(_ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(k_cache), _ptr(v_cache),
+                                      _batch_stride(k_cache), _ptr(tab), B, n, H, D, int(start_idx), f_tied, h_reduce,
+                                      w_reduce, h, w, int(start_frame), 1 if monarch_order else 0, _stream())
+        _lib.check(rc, "sfm_rope_cache_write")
+    return q_rot
+
+
 def rope_monarch_attn_with_kv_cache(q, k, v, k_cache, v_cache, start_idx, end_idx, start_frame, f_tied, h_reduce,
                                     w_reduce, h, w, freqs=None, sm_scale=None, num_iters=1):
     """Fused front end: q, k are the UN-rotated projections.  One kernel applies the 3-axis RoPE
@@ -331,6 +368,24 @@ def full_attention_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, e
                                           int(start_idx), 1, 1, 1, 1, 1, 0, 0, _stream())
     _lib.check(rc, "sfm_rope_cache_write")
     return attention(q, k_cache, v_cache, softmax_scale=sm_scale)
+
+
+def dense_attention_on_cache(q, k_view, v_view, sm_scale=None):
+    """Dense attention of already rotated q against a cache view that already holds the new tokens."""
+    _cache_view_ok(k_view, "k_cache")
+    _cache_view_ok(v_view, "v_cache")
+    return attention(q, k_view, v_view, softmax_scale=sm_scale)
+
+
+def monarch_attention_on_cache(q, k_view, v_view, f_tied, h_reduce, w_reduce, h, w, sm_scale=None, num_iters=1):
+    """Monarch attention of already rotated q against a cache view (Monarch order) that already holds
+    the new tokens: the part of monarch_attn_with_kv_cache after its cache write."""
+    _require(q, "q")
+    _cache_view_ok(k_view, "k_cache")
+    _cache_view_ok(v_view, "v_cache")
+    if sm_scale is None:
+        sm_scale = q.shape[-1] ** -0.5
+    return _monarch_fwd(_as_token_major(q), k_view, v_view, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
 
 
 def causal_rope_apply(x, grid_sizes, freqs, start_frame=0):

@@ -39,6 +39,14 @@ def rope_inputs():
     return randn(rng, 2, 3 * 5 * 7 + 4, 2, 128), (3, 5, 7)
 
 
+def rmsnorm_inputs():
+    """x [2, 11, 3*128] (three heads wide) with a spread of row magnitudes, weight [384], eps."""
+    rng = np.random.default_rng(303)
+    x = randn(rng, 2, 11, 384) * torch.from_numpy(rng.uniform(0.2, 4.0, size=(2, 11, 1)).astype(np.float32))
+    w = torch.from_numpy(rng.uniform(0.5, 1.5, size=384).astype(np.float32))
+    return x, w, 1e-6
+
+
 def cache_case(ci: int, iters: int):
     """Small cache-path case: B=2, H=2, D=32, chunk of 3 frames written at the
     end of a 3-chunk view of a 4-chunk buffer (so the batch stride exceeds the view)."""

@@ -36,11 +36,11 @@ REF = Path(os.environ.get("SF_REFERENCE_ROOT", "/root/reference"))
 def _extract(path: Path, names):
     src = path.read_text()
     tree = ast.parse(src)
-    wanted = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    wanted = [n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef)) and n.name in names]
     missing = set(names) - {n.name for n in wanted}
     if missing:
         raise RuntimeError(f"not found in {path}: {missing}")
-    ns = {"torch": torch, "rearrange": rearrange, "math": math}
+    ns = {"torch": torch, "nn": torch.nn, "rearrange": rearrange, "math": math}
     code = ast.Module(body=wanted, type_ignores=[])
     exec(compile(code, str(path), "exec"), ns)
     return ns
@@ -50,7 +50,7 @@ def load_reference():
     ns = _extract(REF / "wan/modules/monarch_attn.py",
                   ["_get_rearrange_fns", "monarch_attn_slow", "monarch_attn_ref_op",
                    "monarch_attn_with_kv_cache_ref", "monarch_attn_causal_ref"])
-    ns_model = _extract(REF / "wan/modules/model.py", ["rope_params"])
+    ns_model = _extract(REF / "wan/modules/model.py", ["rope_params", "WanRMSNorm"])
     ns_causal = _extract(REF / "wan/modules/causal_model.py", ["causal_rope_apply"])
     return ns, ns_model, ns_causal
 
@@ -167,6 +167,15 @@ def main():
                                     c["sm_scale"], iters)
         out[f"c1_T{iters}_z_sample"] = z[0, ::97, ::5, :].numpy()
         out[f"c1_T{iters}_z_sum"] = np.array([z.double().sum().item(), z.double().abs().sum().item()])
+
+    # ---- 7. full-width RMS normalisation of q / k (WanRMSNorm, model.py:462-478) ----------
+    x, wgt, eps = cases.rmsnorm_inputs()
+    norm = ns_model["WanRMSNorm"](x.shape[-1], eps=eps)
+    with torch.no_grad():
+        norm.weight.copy_(wgt)
+        out["rmsnorm_fp32"] = norm(x).numpy()
+        norm_b = norm.to(torch.bfloat16)
+        out["rmsnorm_bf16"] = norm_b(x.to(torch.bfloat16)).float().numpy()
 
     np.savez_compressed(HERE / "monarch_golden.npz", **out)
     sz = (HERE / "monarch_golden.npz").stat().st_size

@@ -103,3 +103,34 @@ def test_entry_points_validate_arguments_without_a_gpu(sfb):
                                1.0, 1, 0, null) == -2
     assert lib.sfm_rope_cache_write(null, one, one, null, one, one, 0, null, 1, 100, 1, 128, 0, 1, 1, 1, 30, 52,
                                     0, 1, null) == -2
+
+
+def test_plan_cache_step_equals_oracle(sfb):
+    """The product's cache bookkeeping against the oracle's restatement of causal_model.py:907-938,
+    over a random walk of rollouts with and without a sliding window (integers: exact)."""
+    from oracle import monarch_oracle as orc
+    import random
+    rnd = random.Random(5)
+    frame = 1560
+    for trial in range(200):
+        window = rnd.choice([-1, 6, 9, 12, 21])
+        sink = rnd.choice([0, 1, 3]) if window != -1 else 0
+        size = 21 * frame if window == -1 else window * frame
+        max_att = size if rnd.random() < 0.7 else rnd.choice([6, 9]) * frame
+        g_end = l_end = 0
+        chunk = 0
+        for _ in range(rnd.randint(1, 14)):
+            repeat = rnd.random() < 0.5 and chunk > 0       # re-denoise the same chunk: same current_start
+            if not repeat:
+                chunk += 1
+            cur = (chunk - 1) * 3 * frame
+            a = orc.cache_indices(cur, 3 * frame, g_end, l_end, size, max_att, local_attn_size=window,
+                                  sink_tokens=sink * frame)
+            b = sfb.plan_cache_step(cur, 3 * frame, g_end, l_end, size, max_att, local_attn_size=window,
+                                    sink_tokens=sink * frame)
+            assert (b.roll, b.cache_start, b.local_start, b.local_end, b.store_global_end, b.store_local_end) == \
+                   (a["roll"], a["cache_start"], a["local_start"], a["local_end"], a["store_global_end"],
+                    a["store_local_end"])
+            g_end, l_end = b.store_global_end, b.store_local_end
+            if window == -1 and chunk >= 7:
+                break

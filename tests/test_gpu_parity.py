@@ -346,3 +346,166 @@ def test_gather_scatter_shards_match_unsharded(sfb):
         assert torch.equal(vc, vc_ref[:, :, r * hp:(r + 1) * hp])
     got = torch.cat(out_sh, dim=1)
     assert torch.equal(got, ref)
+
+
+# ------------------------------------------------------------------------------- layer level
+@pytest.mark.gpu
+@pytest.mark.parametrize("H", [2, 12])
+def test_norm_rope_cache_write_vs_oracle(sfb, H):
+    """Full-width RMSNorm of q and k + RoPE + Monarch-order cache write in one kernel against the oracle
+    chain rms_norm (reference WanRMSNorm) -> fp64 rotation -> permutation.  bf16 results may differ by one
+    ulp where the fp32 mean of squares sums in another order; v is copied bit for bit."""
+    rng = np.random.default_rng(77 + H)
+    B, h, w = 2, 6, 8
+    n = 3 * h * w
+    q, k, v = (bf(cases.randn(rng, B, n, H, 128) * 1.7) for _ in range(3))
+    wq = bf(torch.from_numpy(rng.uniform(0.5, 1.5, size=H * 128).astype(np.float32)))
+    wk = bf(torch.from_numpy(rng.uniform(0.5, 1.5, size=H * 128).astype(np.float32)))
+    eps = 1e-6
+    kc = torch.zeros(B, 2 * n, H, 128, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q_rot = sfb.norm_rope_cache_write(q.cuda(), k.cuda(), v.cuda(), kc, vc, n, 3, 1, 2, 4, h, w,
+                                      norm_q_weight=wq.cuda(), norm_k_weight=wk.cuda(), eps=eps)
+    torch.cuda.synchronize()
+    nq = orc.rms_norm(q.reshape(B, n, H * 128), wq, eps).reshape(B, n, H, 128)
+    nk = orc.rms_norm(k.reshape(B, n, H * 128), wk, eps).reshape(B, n, H, 128)
+    ref_q = orc.rope_apply(nq, (3, h, w), start_frame=3)
+    ref_k = orc.rope_apply(nk, (3, h, w), start_frame=3)
+    _, mon2nat = orc.token_maps(n, 1, 2, 4, h, w)
+    perm = torch.from_numpy(mon2nat)
+    for got, ref in ((q_rot.cpu(), ref_q), (kc[:, n:].cpu(), ref_k[:, perm])):
+        n_diff, max_ulp = ulp_mismatch(got, ref)
+        assert max_ulp <= 2 and n_diff <= 0.01 * ref.numel(), (n_diff, max_ulp)
+    assert torch.equal(vc[:, n:].cpu(), v[:, perm])
+    assert not kc[:, :n].any() and not vc[:, :n].any()
+
+
+def _oracle_layer_call(state, q, k, v, current_start, grid, cfg, wq, wk):
+    """CPU restatement of the cache branch of CausalWanSelfAttention.forward (causal_model.py:900-1103)
+    from oracle pieces, on fp32 copies of bf16-rounded cache contents."""
+    frames, gh, gw = grid
+    B, n, H, D = q.shape
+    ft = 1 if cfg.use_framewise else 3
+    frame = gh * gw
+    r = orc.cache_indices(current_start, n, state["g_end"], state["l_end"], state["k"].shape[1], cfg.max_attention_size,
+                          local_attn_size=cfg.local_attn_size, sink_tokens=cfg.sink_size * frame)
+    if r["roll"] is not None:
+        dst, src, cnt = r["roll"]
+        for t in (state["k"], state["v"]):
+            t[:, dst:dst + cnt] = t[:, src:src + cnt].clone()
+    nq = orc.rms_norm(q.reshape(B, n, H * D), wq, cfg.eps).reshape(B, n, H, D)
+    nk = orc.rms_norm(k.reshape(B, n, H * D), wk, cfg.eps).reshape(B, n, H, D)
+    rq = orc.rope_apply(nq, grid, start_frame=current_start // frame)
+    rk = orc.rope_apply(nk, grid, start_frame=current_start // frame)
+    ck = state["k"][:, r["cache_start"]:r["cache_start"] + r["local_end"]]
+    cv = state["v"][:, r["cache_start"]:r["cache_start"] + r["local_end"]]
+    is_init = cfg.use_dense_init and ck.shape[1] == 3 * frame
+    if cfg.disable_monarch or is_init:
+        ck[:, r["local_start"]:r["local_end"]] = rk.float()
+        cv[:, r["local_start"]:r["local_end"]] = v.float()
+        out = orc.dense_attention(rq.float(), ck, cv)
+    else:
+        out = orc.monarch_attn_with_kv_cache(rq.float(), ck, cv, rk.float(), v.float(), r["local_start"], r["local_end"],
+                                             ft, cfg.h_reduce, cfg.w_reduce, gh, gw, num_iters=cfg.num_iters)
+    state["g_end"], state["l_end"] = r["store_global_end"], r["store_local_end"]
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["plain", "window_sink", "dense_init", "regular"])
+def test_layer_rollout_matches_oracle(sfb, mode):
+    """Several chunks through self_attention_kv (each chunk denoised twice, as the few-step sampler does)
+    against the oracle's restatement of the reference layer, including the sliding window with a sink frame,
+    the dense first chunk and the all-dense configuration; the caches must agree too."""
+    rng = np.random.default_rng({"plain": 1, "window_sink": 2, "dense_init": 3, "regular": 4}[mode])
+    B, H, gh, gw = 1, 2, 6, 8
+    frame, n = gh * gw, 3 * gh * gw
+    cfg = sfb.LayerConfig(use_framewise=True)
+    cache_frames = 12
+    if mode == "window_sink":
+        cfg.local_attn_size, cfg.sink_size, cache_frames = 9, 1, 9
+    if mode == "dense_init":
+        cfg.use_dense_init = True
+    if mode == "regular":
+        cfg.disable_monarch = True
+    cfg.max_attention_size = cache_frames * frame
+    cache = sfb.KVCache.allocate(B, cache_frames * frame, H, "cuda")
+    state = {"k": torch.zeros(B, cache_frames * frame, H, 128), "v": torch.zeros(B, cache_frames * frame, H, 128),
+             "g_end": 0, "l_end": 0}
+    wq = bf(torch.from_numpy(rng.uniform(0.7, 1.3, size=H * 128).astype(np.float32)))
+    wk = bf(torch.from_numpy(rng.uniform(0.7, 1.3, size=H * 128).astype(np.float32)))
+    n_chunks = 6 if mode == "window_sink" else 4
+    for chunk in range(n_chunks):
+        for rep in range(2):
+            q, k, v = (bf(cases.randn(rng, B, n, H, 128)) for _ in range(3))
+            got = sfb.self_attention_kv(q.cuda(), k.cuda(), v.cuda(), cache, chunk * n, (3, gh, gw), cfg,
+                                        norm_q_weight=wq.cuda(), norm_k_weight=wk.cuda())
+            torch.cuda.synchronize()
+            ref = _oracle_layer_call(state, q, k, v, chunk * n, (3, gh, gw), cfg, wq, wk)
+            check_close(got, ref, f"{mode} chunk {chunk} pass {rep}")
+            assert (cache.global_end, cache.local_end) == (state["g_end"], state["l_end"])
+            # cache contents: rotated keys within bf16 rounding of the oracle's, values identical
+            used = state["l_end"]
+            assert torch.equal(cache.v[:, :used].cpu().float(), state["v"][:, :used])
+            dk = (cache.k[:, :used].cpu().float() - bf(state["k"][:, :used]).float()).abs().max().item()
+            assert dk <= 0.05, dk
+            # keep the two caches in lock step (the oracle's keys are fp32, ours bf16)
+            state["k"][:, :used] = cache.k[:, :used].cpu().float()
+
+
+@pytest.mark.gpu
+def test_patched_forward_on_a_lookalike_module(sfb):
+    """patch_self_attention_forward on a module with the attributes of the reference's
+    CausalWanSelfAttention (the reference itself cannot be imported where the GPU tests run): the patched
+    forward must equal projections -> oracle layer -> output projection, follow a cache reset done the
+    pipeline's way (new index tensors in the dict), and leave the dict's device indices up to date."""
+    from self_forcing_b200.install import patch_self_attention_forward
+    torch.manual_seed(3)
+    dim, H, gh, gw = 256, 2, 6, 8
+    frame, n = gh * gw, 3 * gh * gw
+
+    class Norm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.rand(dim) + 0.5)
+
+    class Attn(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.num_heads, self.head_dim, self.eps = H, dim // H, 1e-6
+            self.use_framewise, self.h_reduce, self.w_reduce, self.num_iters = True, 1, 1, 1
+            self.disable_monarch, self.use_dense_init = False, True
+            self.local_attn_size, self.sink_size, self.max_attention_size = -1, 0, 12 * frame
+            self.topk, self.use_svg, self.use_radial_attn = None, False, False
+            self.q, self.k, self.v, self.o = (torch.nn.Linear(dim, dim) for _ in range(4))
+            self.norm_q, self.norm_k = Norm(), Norm()
+
+        def forward(self, *a, **k):
+            raise AssertionError("the original forward must not be reached on the cache path")
+
+    patch_self_attention_forward(Attn)
+    m = Attn().cuda().to(torch.bfloat16)
+    kv = {"k": torch.zeros(1, 12 * frame, H, 128, dtype=torch.bfloat16, device="cuda"),
+          "v": torch.zeros(1, 12 * frame, H, 128, dtype=torch.bfloat16, device="cuda"),
+          "global_end_index": torch.tensor([0], device="cuda"), "local_end_index": torch.tensor([0], device="cuda")}
+    grid_sizes = torch.tensor([[3, gh, gw]])
+    cfg = sfb.LayerConfig(use_framewise=True, use_dense_init=True, max_attention_size=12 * frame)
+    for video in range(2):
+        state = {"k": torch.zeros(1, 12 * frame, H, 128), "v": torch.zeros(1, 12 * frame, H, 128), "g_end": 0, "l_end": 0}
+        for chunk in range(3):
+            x = torch.randn(1, n, dim).to(torch.bfloat16).cuda()
+            got = m(x, None, grid_sizes, None, None, kv_cache=kv, current_start=chunk * n)
+            torch.cuda.synchronize()
+            q = m.q(x).view(1, n, H, 128).cpu()
+            k = m.k(x).view(1, n, H, 128).cpu()
+            v = m.v(x).view(1, n, H, 128).cpu()
+            ref = _oracle_layer_call(state, q, k, v, chunk * n, (3, gh, gw), cfg, m.norm_q.weight.detach().cpu(),
+                                     m.norm_k.weight.detach().cpu())
+            ref_out = m.o(bf(ref).cuda().flatten(2))
+            err = (got.float() - ref_out.float()).abs().max().item()
+            assert err <= 3e-2, (video, chunk, err)
+            assert kv["global_end_index"].item() == state["g_end"] and kv["local_end_index"].item() == state["l_end"]
+            state["k"][:, :state["l_end"]] = kv["k"][:, :state["l_end"]].cpu().float()
+        # the pipeline's reset: new index tensors, same k / v buffers
+        kv["global_end_index"] = torch.tensor([0], device="cuda")
+        kv["local_end_index"] = torch.tensor([0], device="cuda")

@@ -140,3 +140,11 @@ def test_cache_indices_sliding_window():
             assert r["roll"] == (frame, frame + 3 * frame, 9 * frame - 3 * frame - frame)
             assert r["local_end"] == size and r["local_start"] == size - 3 * frame
         g_end, l_end = r["store_global_end"], r["store_local_end"]
+
+
+def test_rms_norm_matches_reference_class(golden):
+    """oracle.rms_norm against outputs of the reference's own WanRMSNorm (fp32 and bf16 module)."""
+    x, w, eps = cases.rmsnorm_inputs()
+    np.testing.assert_allclose(orc.rms_norm(x, w, eps).numpy(), golden["rmsnorm_fp32"], rtol=1e-6, atol=1e-6)
+    got = orc.rms_norm(x.to(torch.bfloat16), w.to(torch.bfloat16), eps).float().numpy()
+    assert np.array_equal(got, golden["rmsnorm_bf16"])
