@@ -134,9 +134,9 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     p.scale = sm_scale;
     p.blk = pl.blk;
 
-    // Tensor-core path: single pass, no causal mask.  The iterative and block-causal variants run
-    // on the mma.sync kernels.
-    const bool use_tc = (num_iters == 1 && causal_groups == 0);
+    // Tensor-core path: single pass (block-causal included, for block rows up to 128).  The iterative
+    // variant runs on the mma.sync kernels.
+    const bool use_tc = num_iters == 1 && (causal_groups == 0 || pl.blk.b1 <= 128);
     // only the tensor-core column step knows how to scatter its rows
     if (os && os->world > 1 && !(use_tc && pl.blk.b1 <= 128)) return SFM_ERR_UNSUPPORTED;
     int num_sms = 148;
@@ -184,6 +184,16 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
         p.bh0 = bh0; p.nbh = std::min(pl.nbh_chunk, BH - bh0);
         for (int a0 = 0; a0 < pl.A; a0 += pl.na_chunk) {
             p.a0 = a0; p.na = std::min(pl.na_chunk, pl.A - a0);
+            if (use_tc && causal_groups > 0) {
+                // Block-causal: the row step skips the (query group, f) pairs no query may see, so the
+                // column step finds bridge rows nobody wrote.  Give them defined contents: zero keys /
+                // values and the "masked" bias.
+                const size_t rows = (size_t)p.nbh * p.na * pl.blk.b2;
+                cudaError_t e = cudaMemsetAsync(p.aL, 0, rows * pl.n_keys * kHeadDim * 2, stream);
+                if (e == cudaSuccess) e = cudaMemsetAsync(p.Y, 0, rows * pl.n_keys * kHeadDim * 2, stream);
+                if (e == cudaSuccess) e = cudaMemsetAsync(p.cL, 0x7f, rows * p.n_keys_c * sizeof(float), stream);
+                if (e != cudaSuccess) return (int)e;
+            }
             // enough row-step CTAs to fill the GPU about twice over
             int asubs = use_tc ? (p.na + (128 / rows_per_group) - 1) / (128 / rows_per_group)
                                : (p.na + p.na_cta - 1) / p.na_cta;

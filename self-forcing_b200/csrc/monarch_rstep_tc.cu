@@ -77,7 +77,13 @@ __device__ __forceinline__ RUnit decode_unit(const RTcParams& rp, int u) {
     r.tile = u % rp.tiles;
     r.bhl = u / rp.tiles;
     r.f_begin = fs * p.f_per;
-    r.n_it = min(p.F, r.f_begin + p.f_per) - r.f_begin;
+    int f_end = min(p.F, r.f_begin + p.f_per);
+    if (p.causal_groups > 0) {
+        // block-causal (no-cache path): the tile's last query group sees the most; later groups f are skipped
+        const int a_hi = p.a0 + min((r.tile + 1) * rp.groups_per_tile, p.na) - 1;
+        f_end = min(f_end, (a_hi / p.causal_groups + 1) * p.causal_groups);
+    }
+    r.n_it = max(0, f_end - r.f_begin);               // 0: nothing to do, every role skips the unit
     return r;
 }
 
@@ -165,8 +171,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         if (lane == 0) {
             prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv);
             int g = 0, uc = 0;
-            for (int u = u_first; u < rp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+            for (int u = u_first; u < rp.n_units && !bars->abort_flag; u += u_stride) {
                 const RUnit un = decode_unit(rp, u);
+                if (un.n_it == 0) continue;
                 const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
                 const int g_first = un.tile * rp.groups_per_tile;
                 const int ng = min(rp.groups_per_tile, p.na - g_first);
@@ -190,6 +197,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     tma_load_4d(st + 2 * kHalf, &tv, &bars->kv_full[s], 0, hd, tok, b);
                     tma_load_4d(st + 3 * kHalf, &tv, &bars->kv_full[s], 64, hd, tok, b);
                 }
+                ++uc;
             }
         }
     } else if (warp == 2) {
@@ -202,8 +210,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             const uint64_t k_desc0 = smem_desc_sw128(smem_addr(kv_s), 16, 1024);
             int g = 0, uc = 0;
             bool ok = true;
-            for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride, ++uc) {
+            for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
                 const RUnit un = decode_unit(rp, u);
+                if (un.n_it == 0) continue;
                 if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStages;
@@ -221,6 +230,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     mma_commit(&bars->s_full[g & 1]);
                     if (i + 1 == un.n_it) mma_commit(&bars->q_empty);   // last read of this unit's Q tile
                 }
+                ++uc;
             }
         }
     } else if (warp == 1) {
@@ -270,6 +280,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             const bool warp_active = quad * 32 < ng * RG;
             const bool row_ok = gl < ng && j < b2;
             const long long aj = ((long long)un.bhl * p.na + g_first + gl) * b2 + j;
+            // block-causal: groups f this row's query group may not see get an infinite bias
+            const int f_allowed = p.causal_groups > 0
+                ? ((p.a0 + g_first + gl) / p.causal_groups + 1) * p.causal_groups : p.F;
             for (int i = 0; i < un.n_it; ++i, ++g) {
                 if ((g & 1) != wg) continue;
                 if (lane == 0 && quad == 0) TRACE(2, g, 0);
@@ -334,7 +347,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     if (lane == 0 && quad == 0) TRACE(6, g, 2);
                     if (row_ok) {
                         const int key = (un.f_begin + i) * b1 + un.k;
-                        p.cL[aj * p.n_keys_c + key] = 0.6931471805599453f * ent * inv_z - __logf(z);
+                        p.cL[aj * p.n_keys_c + key] =
+                            un.f_begin + i < f_allowed ? 0.6931471805599453f * ent * inv_z - __logf(z) : INFINITY;
                     }
                 }
                 tc_fence_before();

@@ -94,8 +94,12 @@ def test_cache_write_real_grid_bit_exact(sfb):
     assert not kc[:, :n].any() and not vc[:, :n].any()
 
 
-def ulp_mismatch(a, b):
-    """Count of elements differing, and max difference in bf16 ulps (via the int16 bit patterns)."""
+def ulp_mismatch(a, b, tiny=1e-3, tiny_abs=1e-6):
+    """Count of elements differing, and max difference in bf16 ulps (via the int16 bit patterns).
+    Results below `tiny` in magnitude come from cancelling terms of order one (a rotation in fp32
+    here, fp64 in the reference) and are compared by absolute difference instead."""
+    small = (b.float().abs() < tiny) & ((a.float() - b.float()).abs() <= tiny_abs)
+    a = torch.where(small, b, a)
     ai = a.contiguous().view(torch.int16).to(torch.int32)
     bi = b.contiguous().view(torch.int16).to(torch.int32)
     # sign-magnitude -> monotonic integer
