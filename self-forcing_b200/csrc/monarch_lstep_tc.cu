@@ -111,9 +111,6 @@ __device__ __forceinline__ void mma_ts_masked(uint32_t d_tmem, uint32_t a_tmem, 
 struct LUnit { int bhl, al, j; };
 __device__ __forceinline__ LUnit decode_unit(const MonarchParams& p, int u) {
     LUnit r;
-#ifdef SFM_L_REVERSE
-    u = p.nbh * p.na * p.blk.b2 - 1 - u;
-#endif
     r.j = u % p.blk.b2; u /= p.blk.b2;
     r.al = u % p.na;
     r.bhl = u / p.na;
@@ -618,9 +615,6 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
     lp.U = 32 / lp.R4;
     if (lp.U < 1) lp.U = 1;
     if (lp.U > kMaxU) lp.U = kMaxU;
-#ifdef SFM_L_CAPU
-    if (lp.U > SFM_L_CAPU) lp.U = SFM_L_CAPU;
-#endif
     lp.status = status;
     // Query rows that are consecutive rows of the token grid come by TMA (the 128-byte swizzle is a function
     // of the shared-memory address, so a box may land on any 128-byte row of the tile); other blockings

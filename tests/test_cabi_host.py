@@ -103,6 +103,29 @@ def test_entry_points_validate_arguments_without_a_gpu(sfb):
                                1.0, 1, 0, null) == -2
     assert lib.sfm_rope_cache_write(null, one, one, null, one, one, 0, null, 1, 100, 1, 128, 0, 1, 1, 1, 30, 52,
                                     0, 1, null) == -2
+    # fused RMSNorm front end: both weights and q are required
+    assert lib.sfm_norm_rope_cache_write(one, one, one, null, one, 1e-6, one, one, one, 0, null, 1, 1560, 1, 128, 0,
+                                         1, 1, 1, 30, 52, 0, 1, null) == -1
+    assert lib.sfm_norm_rope_cache_write(null, one, one, one, one, 1e-6, one, one, one, 0, null, 1, 1560, 1, 128, 0,
+                                         1, 1, 1, 30, 52, 0, 1, null) == -1
+    # head-sharded entry points: rank / world range, shard pointers, divisibility of the chunk
+    ptrs = (C.c_void_p * 2)(256, 512)
+    holes = (C.c_void_p * 2)(256, 0)
+    assert lib.sfm_rope_cache_write_gather(ptrs, ptrs, ptrs, 9, 0, one, one, one, 0, null, 1, 1560, 1, 128, 0,
+                                           1, 1, 1, 30, 52, 0, 1, null) == -2
+    assert lib.sfm_rope_cache_write_gather(ptrs, ptrs, ptrs, 2, 2, one, one, one, 0, null, 1, 1560, 1, 128, 0,
+                                           1, 1, 1, 30, 52, 0, 1, null) == -2
+    assert lib.sfm_rope_cache_write_gather(ptrs, holes, ptrs, 2, 0, one, one, one, 0, null, 1, 1560, 1, 128, 0,
+                                           1, 1, 1, 30, 52, 0, 1, null) == -1
+    assert lib.sfm_rope_cache_write_gather(ptrs, ptrs, ptrs, 2, 0, one, one, one, 0, null, 1, 1561, 1, 128, 0,
+                                           1, 1, 1, 30, 52, 0, 1, null) == -2
+    assert lib.sfm_monarch_fwd_scatter(one, 0, one, one, 0, holes, 2, 0, one, 1 << 30, 1, 1, 128, 1560, 1560,
+                                       1, 1, 1, 30, 52, 1.0, 0, null) == -1
+    assert lib.sfm_monarch_fwd_scatter(one, 0, one, one, 0, ptrs, 2, 5, one, 1 << 30, 1, 1, 128, 1560, 1560,
+                                       1, 1, 1, 30, 52, 1.0, 0, null) == -2
+    # block rows above 128 (tied3frame at 480p: 90 is fine; 3 x 60 = 180 is not) cannot scatter
+    assert lib.sfm_monarch_fwd_scatter(one, 0, one, one, 0, ptrs, 2, 0, one, 1 << 34, 1, 1, 128, 3 * 60 * 52,
+                                       3 * 60 * 52, 3, 1, 1, 60, 52, 1.0, 0, null) == -3
 
 
 def test_plan_cache_step_equals_oracle(sfb):
