@@ -105,19 +105,10 @@ constexpr int kQBytes = 2 * kTileRows * 128;               // two 64-column halv
 constexpr int kStageBytes = 4 * 64 * 128;                  // K half 0, K half 1, V half 0, V half 1 (<= 64 rows each)
 constexpr int kSmemBytes = 1024 + kQBytes + kStages * kStageBytes + 256;
 
-// Register budget per warpgroup (the kernel launches with 640 threads at 96 registers each): the
-// control warpgroup gives registers back, the compute warpgroups take more.
-template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-
 // 32-byte store of 16 bf16 to global memory (pointer 32-byte aligned).
 __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
     asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
                  "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-}
-
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 template <int N_S>

@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) primitives used by the tensor-core kernels: mbarriers with bounded waits,
-// TMA tiled loads/stores, tensor-memory (TMEM) allocation and access, tcgen05.mma issue and the
+// TMA tiled loads, tensor-memory (TMEM) allocation and access, tcgen05.mma issue and the
 // shared-memory / instruction descriptors it takes.  Inline PTX only.
 #pragma once
 #include <cuda.h>
@@ -82,25 +82,6 @@ __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
-}
-// 3-D / 4-D tiled store shared -> global, tracked by the bulk async-group of the issuing thread.
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_addr(smem_src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_addr(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {   // sources of all but the N newest groups may be reused
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all() {
-    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 // Make generic-proxy writes to shared memory visible to the async proxy (TMA / tcgen05.mma reads).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
