@@ -140,7 +140,18 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b1 = blk.b1, b2 = blk.b2;
     const int n_keys = kDense ? lp.n_kv : p.n_keys;
-    const int n_tiles = (n_keys + kKT - 1) / kKT;
+    const int n_tiles_all = (n_keys + kKT - 1) / kKT;
+    // Key tiles a group of units has to walk.  Block-causal (no-cache path): the keys past the last cached
+    // group any of the group's units may see carry an infinite bias, so the walk stops before them.
+    auto group_tiles = [&](int u0, int nu) -> int {
+        if (kDense || p.causal_groups <= 0) return n_tiles_all;
+        int fmax = 0;
+        for (int us = 0; us < nu; ++us) {
+            const int a_abs = p.a0 + decode_unit(p, u0 + us).al;
+            fmax = max(fmax, min(p.F, (a_abs / p.causal_groups + 1) * p.causal_groups));
+        }
+        return (fmax * b1 + kKT - 1) / kKT;
+    };
     const long long tok_pitch = (long long)p.H * kHeadDim;
     const int U = lp.U, R4 = lp.R4;
     // this CTA's contiguous share of the unit list, walked in groups of at most U units
@@ -206,6 +217,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         bool ok = true;
         for (int u0 = u_begin; ok && u0 < u_end && !bars->abort_flag; u0 += u_step, ++gc) {
             const int nu = kDense ? 1 : min(U, u_end - u0);
+            const int n_tiles = group_tiles(u0, nu);
             if (gc > 0) {
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(&bars->q_empty, (gc - 1) & 1) ? 1 : 0;
@@ -310,6 +322,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             bool ok = true;
             for (int u0 = u_begin; ok && u0 < u_end && !bars->abort_flag; u0 += u_step) {
                 const int nu = kDense ? 1 : min(U, u_end - u0);
+            const int n_tiles = group_tiles(u0, nu);
                 for (int t = 0; ok && t < n_tiles; ++t)
                     for (int us = 0; us < nu; ++us, ++gy) {
                         const int sy = gy % kYStages;
@@ -341,6 +354,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             bool ok = true;
             for (int u0 = u_begin; ok && u0 < u_end && !bars->abort_flag; u0 += u_step, ++gc) {
                 const int nu = kDense ? 1 : min(U, u_end - u0);
+            const int n_tiles = group_tiles(u0, nu);
                 if (!mbar_wait(&bars->q_full, gc & 1)) { fail(20); break; }
                 for (int t = 0; ok && t < n_tiles; ++t) {
                     const int w = t & 1;
@@ -380,6 +394,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             bool ok = true;
             for (int u0 = u_begin; ok && u0 < u_end && !bars->abort_flag; u0 += u_step, ++gc) {
                 const int nu = kDense ? 1 : min(U, u_end - u0);
+            const int n_tiles = group_tiles(u0, nu);
                 for (int t = 0; ok && t < n_tiles; ++t) {
                     const int w = t & 1;
                     const int idx = cnt[w]++;
@@ -428,6 +443,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         int gc = 0, idx = 0;                  // idx: tiles this warpgroup has handled so far
         bool ok = true;
         for (int u0 = u_begin; ok && u0 < u_end && !bars->abort_flag; u0 += u_step, ++gc) {
+            const int n_tiles = group_tiles(u0, kDense ? 1 : min(U, u_end - u0));
             float m_run = -INFINITY, l_run = 0.f;
             int my_tiles = 0;
             for (int t = w; t < n_tiles; t += 2) {
@@ -533,6 +549,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         int gc = 0;
         for (int u0 = u_begin; u0 < u_end && !bars->abort_flag; u0 += u_step, ++gc) {
             const int nu = kDense ? 1 : min(U, u_end - u0);
+            const int n_tiles = group_tiles(u0, nu);
             if (!mbar_wait(&bars->o_full, gc & 1)) { fail(41); break; }
             tc_fence_after();
             // even tiles went to warpgroup 0, odd tiles to warpgroup 1

@@ -114,8 +114,7 @@ __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) 
 template <int N_S>
 __global__ void __launch_bounds__(kThreads, 1)
 monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tal,
-                    const __grid_constant__ CUtensorMap ty, RTcParams rp) {
+                    const __grid_constant__ CUtensorMap tv, RTcParams rp) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
@@ -424,7 +423,7 @@ extern "C" void sfm_debug_set_ablate(int a) { g_sfm_ablate = a; }
 
 // Launches the tensor-core row step for one chunk as a persistent grid.  `status` is a device int the
 // kernel sets on an internal timeout.
-int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q,k,v,aL,Y */, int rows_per_group, int n_s,
+int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v */, int rows_per_group, int n_s,
                      int* status, int num_sms, cudaStream_t s) {
     LaunchScope scope(kClsRStep, s);
     RTcParams rp;
@@ -442,7 +441,7 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q,k,v,aL
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
-        kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], rp);
+        kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], rp);
         return 0;
     };
     int rc;

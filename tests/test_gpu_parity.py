@@ -513,3 +513,48 @@ def test_patched_forward_on_a_lookalike_module(sfb):
         # the pipeline's reset: new index tensors, same k / v buffers
         kv["global_end_index"] = torch.tensor([0], device="cuda")
         kv["local_end_index"] = torch.tensor([0], device="cuda")
+
+
+# ------------------------------------------------------------------------------- seeded shape sweep
+def _sweep_configs():
+    """Seeded mix of shapes the other tests do not pair up: odd head counts, two videos with a cache batch
+    stride longer than the view, query chunks of 3 to 6 frames, 1 to 5 cached chunks, grids whose block rows
+    and columns land on every padding case of the kernels (b2 from 2 to 48, b1 from 3 to 36)."""
+    import random
+    rnd = random.Random(2024)
+    grids = [(6, 8), (4, 12), (12, 16), (8, 48), (5, 7), (10, 26)]
+    out = []
+    for _ in range(18):
+        h, w = rnd.choice(grids)
+        ft = rnd.choice([1, 3])
+        hr = rnd.choice([d for d in (1, 2, 3, 4, 5) if h % d == 0])
+        wr = rnd.choice([d for d in (1, 2, 4, 13) if w % d == 0])
+        frames_q = 3 * rnd.choice([1, 2])
+        cached = rnd.randint(1, 5)
+        out.append(dict(h=h, w=w, ft=ft, hr=hr, wr=wr, frames_q=frames_q, cached=cached, B=rnd.choice([1, 2]),
+                        H=rnd.choice([1, 2, 3, 5]), T=rnd.choice([1, 1, 1, 2]), seed=rnd.randrange(1 << 30)))
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", _sweep_configs(), ids=lambda c: "h{h}w{w}_ft{ft}hr{hr}wr{wr}_q{frames_q}c{cached}_B{B}H{H}T{T}".format(**c))
+def test_monarch_seeded_shape_sweep(sfb, cfg):
+    rng = np.random.default_rng(cfg["seed"])
+    h, w, B, H = cfg["h"], cfg["w"], cfg["B"], cfg["H"]
+    frame = h * w
+    n_q = cfg["frames_q"] * frame
+    n_kv = cfg["cached"] * 3 * frame + n_q
+    n_buf = n_kv + 3 * frame                                  # the view is shorter than the buffer
+    mk = lambda *s: bf(cases.randn(rng, *s))
+    q, nk, nv = mk(B, n_q, H, 128), mk(B, n_q, H, 128), mk(B, n_q, H, 128)
+    kbuf, vbuf = mk(B, n_buf, H, 128), mk(B, n_buf, H, 128)
+    blocking = (cfg["ft"], cfg["hr"], cfg["wr"], h, w)
+    kc, vc = kbuf.float().clone(), vbuf.float().clone()
+    ref = orc.monarch_attn_with_kv_cache(q.float(), kc[:, :n_kv], vc[:, :n_kv], nk.float(), nv.float(), n_kv - n_q, n_kv,
+                                         *blocking, num_iters=cfg["T"])
+    kg, vg = kbuf.cuda().clone(), vbuf.cuda().clone()
+    got = sfb.monarch_attn_with_kv_cache(q.cuda(), kg[:, :n_kv], vg[:, :n_kv], nk.cuda(), nv.cuda(), n_kv - n_q, n_kv,
+                                         *blocking, num_iters=cfg["T"])
+    torch.cuda.synchronize()
+    check_close(got, ref, str(cfg))
+    assert torch.equal(kg.cpu().float(), kc) and torch.equal(vg.cpu().float(), vc)
