@@ -199,8 +199,20 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                                : (p.na + p.na_cta - 1) / p.na_cta;
             int base_ctas = pl.blk.b1 * asubs * p.nbh;
             int fsplit;
-            if (use_tc) {   // persistent CTAs: about three units per SM, at least four steps per unit
-                fsplit = std::max(1, std::min(std::max(1, pl.F / 4), (3 * num_sms + base_ctas - 1) / base_ctas));
+            if (use_tc) {
+                // Persistent CTAs take whole units round-robin, so the launch lasts (units per CTA, rounded
+                // up) x (steps per unit).  Pick the split of the F loop that makes that smallest, with at
+                // least three steps per unit (every unit reloads its query tile) and an extra step's worth
+                // charged per unit for that reload.
+                fsplit = 1;
+                long long best = -1;
+                for (int fs = 1; fs <= std::max(1, pl.F / 3); ++fs) {
+                    const int per = (pl.F + fs - 1) / fs;
+                    const int splits = (pl.F + per - 1) / per;
+                    const long long units = (long long)base_ctas * splits;
+                    const long long cost = ((units + num_sms - 1) / num_sms) * (per + 1);
+                    if (best < 0 || cost < best) { best = cost; fsplit = fs; }
+                }
             } else {
                 fsplit = std::max(1, std::min(pl.F, (2 * num_sms + base_ctas - 1) / base_ctas));
             }

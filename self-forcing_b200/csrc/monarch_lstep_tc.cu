@@ -119,7 +119,7 @@ __device__ __forceinline__ LUnit decode_unit(const MonarchParams& p, int u) {
 
 // Column step: tal / ty = bridge aL / Y maps (box 64 x 128 keys x 1), tqr = query rows (5-D).
 // Dense:       tal / ty = K / V cache maps (4-D, box 64 x 1 x 128 tokens x 1), tqr = q map (same geometry).
-template <bool kDense>
+template <bool kDense, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_constant__ CUtensorMap ty,
                     const __grid_constant__ CUtensorMap tqr, LTcParams lp) {
@@ -144,7 +144,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     // Key tiles a group of units has to walk.  Block-causal (no-cache path): the keys past the last cached
     // group any of the group's units may see carry an infinite bias, so the walk stops before them.
     auto group_tiles = [&](int u0, int nu) -> int {
-        if (kDense || p.causal_groups <= 0) return n_tiles_all;
+        if (!kCausal) return n_tiles_all;
         int fmax = 0;
         for (int us = 0; us < nu; ++us) {
             const int a_abs = p.a0 + decode_unit(p, u0 + us).al;
@@ -644,9 +644,10 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
 #endif
     const int n_groups = (lp.n_units + lp.U - 1) / lp.U;
     dim3 grid(n_groups < num_sms ? n_groups : num_sms);
-    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    auto kernel = p.causal_groups > 0 ? monarch_l_tc_kernel<false, true> : monarch_l_tc_kernel<false, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    monarch_l_tc_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
+    kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
     return (int)cudaGetLastError();
 }
 
@@ -673,9 +674,9 @@ int launch_dense_tc(const CUtensorMap* maps, __nv_bfloat16* out, int B, int H, i
     lp.trace = nullptr;
 #endif
     dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
-    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    monarch_l_tc_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
+    monarch_l_tc_kernel<true, false><<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], lp);
     return (int)cudaGetLastError();
 }
 

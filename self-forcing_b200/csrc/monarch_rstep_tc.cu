@@ -69,6 +69,7 @@ struct RUnit {
     int bhl, tile, k, f_begin, n_it;
 };
 
+template <bool kCausal>
 __device__ __forceinline__ RUnit decode_unit(const RTcParams& rp, int u) {
     const MonarchParams& p = rp.mp;
     RUnit r;
@@ -78,7 +79,7 @@ __device__ __forceinline__ RUnit decode_unit(const RTcParams& rp, int u) {
     r.bhl = u / rp.tiles;
     r.f_begin = fs * p.f_per;
     int f_end = min(p.F, r.f_begin + p.f_per);
-    if (p.causal_groups > 0) {
+    if (kCausal) {
         // block-causal (no-cache path): the tile's last query group sees the most; later groups f are skipped
         const int a_hi = p.a0 + min((r.tile + 1) * rp.groups_per_tile, p.na) - 1;
         f_end = min(f_end, (a_hi / p.causal_groups + 1) * p.causal_groups);
@@ -111,7 +112,7 @@ __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) 
                  "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 
-template <int N_S>
+template <int N_S, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, RTcParams rp) {
@@ -162,8 +163,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv);
             int g = 0, uc = 0;
             for (int u = u_first; u < rp.n_units && !bars->abort_flag; u += u_stride) {
-                const RUnit un = decode_unit(rp, u);
-                if (un.n_it == 0) continue;
+                const RUnit un = decode_unit<kCausal>(rp, u);
+                if (kCausal && un.n_it == 0) continue;
                 const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
                 const int g_first = un.tile * rp.groups_per_tile;
                 const int ng = min(rp.groups_per_tile, p.na - g_first);
@@ -201,8 +202,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             int g = 0, uc = 0;
             bool ok = true;
             for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
-                const RUnit un = decode_unit(rp, u);
-                if (un.n_it == 0) continue;
+                const RUnit un = decode_unit<kCausal>(rp, u);
+                if (kCausal && un.n_it == 0) continue;
                 if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStages;
@@ -232,7 +233,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             int g = 0;
             bool ok = true;
             for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
-                const RUnit un = decode_unit(rp, u);
+                const RUnit un = decode_unit<kCausal>(rp, u);
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     TRACE(1, g, 0);
                     if (!mbar_wait(&bars->p_full[g & 1], (g >> 1) & 1)) { fail(22); ok = false; break; }
@@ -264,15 +265,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         int g = 0;
         bool ok = true;
         for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
-            const RUnit un = decode_unit(rp, u);
+            const RUnit un = decode_unit<kCausal>(rp, u);
             const int g_first = un.tile * rp.groups_per_tile;
             const int ng = min(rp.groups_per_tile, p.na - g_first);
             const bool warp_active = quad * 32 < ng * RG;
             const bool row_ok = gl < ng && j < b2;
             const long long aj = ((long long)un.bhl * p.na + g_first + gl) * b2 + j;
             // block-causal: groups f this row's query group may not see get an infinite bias
-            const int f_allowed = p.causal_groups > 0
-                ? ((p.a0 + g_first + gl) / p.causal_groups + 1) * p.causal_groups : p.F;
+            const int f_allowed = kCausal ? ((p.a0 + g_first + gl) / p.causal_groups + 1) * p.causal_groups : p.F;
             for (int i = 0; i < un.n_it; ++i, ++g) {
                 if ((g & 1) != wg) continue;
                 if (lane == 0 && quad == 0) TRACE(2, g, 0);
@@ -338,7 +338,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     if (row_ok) {
                         const int key = (un.f_begin + i) * b1 + un.k;
                         p.cL[aj * p.n_keys_c + key] =
-                            un.f_begin + i < f_allowed ? 0.6931471805599453f * ent * inv_z - __logf(z) : INFINITY;
+                            (!kCausal || un.f_begin + i < f_allowed) ? 0.6931471805599453f * ent * inv_z - __logf(z) : INFINITY;
                     }
                 }
                 tc_fence_before();
@@ -355,7 +355,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         int g = 0;
         bool ok = true;
         for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
-            const RUnit un = decode_unit(rp, u);
+            const RUnit un = decode_unit<kCausal>(rp, u);
             const int g_first = un.tile * rp.groups_per_tile;
             const int ng = min(rp.groups_per_tile, p.na - g_first);
             const bool warp_active = quad * 32 < ng * RG;
@@ -445,11 +445,12 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v 
         return 0;
     };
     int rc;
+    const bool causal = p.causal_groups > 0;
     switch (n_s) {
-        case 16: rc = go(monarch_r_tc_kernel<16>); break;
-        case 32: rc = go(monarch_r_tc_kernel<32>); break;
-        case 48: rc = go(monarch_r_tc_kernel<48>); break;
-        case 64: rc = go(monarch_r_tc_kernel<64>); break;
+        case 16: rc = causal ? go(monarch_r_tc_kernel<16, true>) : go(monarch_r_tc_kernel<16, false>); break;
+        case 32: rc = causal ? go(monarch_r_tc_kernel<32, true>) : go(monarch_r_tc_kernel<32, false>); break;
+        case 48: rc = causal ? go(monarch_r_tc_kernel<48, true>) : go(monarch_r_tc_kernel<48, false>); break;
+        case 64: rc = causal ? go(monarch_r_tc_kernel<64, true>) : go(monarch_r_tc_kernel<64, false>); break;
         default: return SFM_ERR_UNSUPPORTED;
     }
     if (rc) return rc;
