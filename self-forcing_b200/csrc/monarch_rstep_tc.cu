@@ -297,26 +297,39 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     // only the last 16 columns can lie beyond b2
 #pragma unroll
                     for (int c = N_S - 16; c < N_S; ++c)
-                        if (c >= b2) raw[c] = 0xff800000u;   // -inf
+                        if (c >= b2) raw[c] = 0xf149f2cau;   // -1e30: exp2 gives 0 and 0 * (finite) stays 0 below
                     float mx = -INFINITY;
 #pragma unroll
-                    for (int c = 0; c < N_S; ++c) mx = fmaxf(mx, __uint_as_float(raw[c]));
+                    for (int c = 0; c < N_S; c += 2) mx = max3(mx, __uint_as_float(raw[c]), __uint_as_float(raw[c + 1]));
                     const float neg_m = -mx * scale_l2;
-                    float z = 0.f, ent = 0.f;
+                    // two columns at a time on the packed fp32 pipe
+                    const uint64_t scale2 = f2_pack(scale_l2, scale_l2), negm2 = f2_pack(neg_m, neg_m);
+                    uint64_t z2 = f2_pack(0.f, 0.f), ent2 = z2;
+                    uint64_t e2[N_S / 2];
 #pragma unroll
-                    for (int c = 0; c < N_S; ++c) {
-                        float d = fmaf(__uint_as_float(raw[c]), scale_l2, neg_m);   // log2 units, <= 0 (-inf if masked)
-                        float e = exp2f(d);
-                        z += e;
-                        ent = fmaf(e, fmaxf(d, -1e30f), ent);                        // masked: 0 * (-1e30) = 0
-                        raw[c] = __float_as_uint(e);
+                    for (int c = 0; c < N_S / 2; ++c) {
+                        const uint64_t d2 = f2_fma(f2_pack(__uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1])), scale2, negm2);
+                        float d0, d1;                         // log2 units, <= 0 (about -1e29 if masked)
+                        f2_unpack(d2, d0, d1);
+                        e2[c] = f2_pack(exp2f(d0), exp2f(d1));
+                        z2 = f2_add(z2, e2[c]);
+                        ent2 = f2_fma(e2[c], d2, ent2);       // masked: 0 * (-1e29) = 0
                     }
+                    float z, zh, ent, enth;
+                    f2_unpack(z2, z, zh);
+                    f2_unpack(ent2, ent, enth);
+                    z += zh;
+                    ent += enth;
                     const float inv_z = 1.0f / z;
                     if (lane == 0 && quad == 0) TRACE(6, g, 1);
+                    const uint64_t invz2 = f2_pack(inv_z, inv_z);
                     uint32_t pk[N_S / 2];
 #pragma unroll
-                    for (int c = 0; c < N_S / 2; ++c)
-                        pk[c] = pack_bf16_alu(__uint_as_float(raw[2 * c]) * inv_z, __uint_as_float(raw[2 * c + 1]) * inv_z);
+                    for (int c = 0; c < N_S / 2; ++c) {
+                        float p0, p1;
+                        f2_unpack(f2_mul(e2[c], invz2), p0, p1);
+                        pk[c] = pack_bf16_alu(p0, p1);
+                    }
                     if constexpr (N_S == 64) {
                         tmem_st32(s_t, pk);
                     } else if constexpr (N_S == 32) {
