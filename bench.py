@@ -44,8 +44,8 @@ N_LAYER_CACHES = 4                              # rotated so K/V (201 MB per lay
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each kernel at the bench
 # workload, from the ncu capture summarised in profiles/monarch_framewise_k7_ncu.md.
-NCU_TRAFFIC = {("framewise", 7): {"monarch_row_step": 262.5e6 + 565.3e6, "monarch_col_step": 624.0e6 + 13.4e6,
-                                  "layout_rope_cache_write": 43.2e6 + 4.6e6}}
+NCU_TRAFFIC = {("framewise", 7): {"monarch_row_step": 267.8e6 + 566.2e6, "monarch_col_step": 624.1e6 + 13.4e6,
+                                  "layout_rope_cache_write": 43.2e6 + 4.3e6}}
 
 
 def algorithmic(blocking: str, k: int, heads: int = HEADS, batch: int = 1):
