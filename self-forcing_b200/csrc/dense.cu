@@ -25,6 +25,7 @@ extern "C" int sfm_dense_fwd(const void* q, int64_t q_batch_stride, const void* 
     if (!q || !k || !v || !out) return SFM_ERR_NULL_POINTER;
     if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
     if (B <= 0 || H <= 0 || n_q <= 0 || n_kv <= 0) return SFM_ERR_BAD_SHAPE;
+    if (!(sm_scale > 0.f)) return SFM_ERR_BAD_SHAPE;       // the row maximum is taken before scaling
     auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
     if (mis(q) || mis(k) || mis(v) || mis(out) || (q_batch_stride % 8) || (kv_batch_stride % 8)) return SFM_ERR_ALIGNMENT;
 

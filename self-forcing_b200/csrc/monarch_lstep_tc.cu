@@ -456,20 +456,33 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 if (!kDense && !mbar_wait(&bars->cl_full[cslot], (idx >> 1) & 1)) { fail(33); ok = false; break; }
                 tc_fence_after();
                 // pass 1: row maximum of the biased logits (log2 units)
+                const bool tail = kDense && valid < kKT;
+                const uint64_t scale2 = f2_pack(scale_l2, scale_l2), nl2 = f2_pack(-kLog2e, -kLog2e);
                 float mx = -INFINITY;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kKT; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld32(s_t + c0, r);
                     tmem_wait_ld();
+                    if (kDense && !tail) {
+                        // no bias: the maximum of the raw dot products (the scale is positive), two per instruction
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        float x = kDense ? __uint_as_float(r[c]) * scale_l2
-                                         : fmaf(__uint_as_float(r[c]), scale_l2, -kLog2e * cs[c0 + c]);
-                        if (kDense && c0 + c >= valid) x = -INFINITY;        // keys past the end of the cache view
-                        mx = fmaxf(mx, x);
+                        for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+                    } else if (kDense) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)                         // keys past the end of the cache view
+                            mx = fmaxf(mx, c0 + c < valid ? __uint_as_float(r[c]) : -INFINITY);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {                    // packed fp32 pairs: S * scale - log2(e) * cL
+                            const uint64_t bias2 = f2_mul(nl2, *reinterpret_cast<const uint64_t*>(&cs[c0 + c]));
+                            float x0, x1;
+                            f2_unpack(f2_fma(f2_pack(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, bias2), x0, x1);
+                            mx = max3(mx, x0, x1);
+                        }
                     }
                 }
+                if (kDense) mx *= scale_l2;
                 // lazy rescale: keep the old reference while the maximum grew by less than the threshold
                 bool rescale = false;
                 float corr = 1.0f;
@@ -499,7 +512,8 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 if (row == 0) LTRACE(2 + w, idx, 2);
                 const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
                 // pass 2: P = exp2(logit - m), packed bf16 written back over the S columns already consumed
-                float lsum = 0.f;
+                const uint64_t negm2 = f2_pack(neg_m, neg_m);
+                uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll 1
                 for (int c0 = 0; c0 < kKT; c0 += 32) {
                     uint32_t r[32];
@@ -508,22 +522,24 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     uint32_t pk[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        float e0, e1;
-                        if (kDense) {
-                            e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, neg_m));
-                            e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, neg_m));
+                        uint64_t shift2 = negm2;
+                        if (!kDense) shift2 = f2_fma(nl2, *reinterpret_cast<const uint64_t*>(&cs[c0 + c]), negm2);
+                        float d0, d1;
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, shift2), d0, d1);
+                        float e0 = exp2f(d0), e1 = exp2f(d1);
+                        if (tail) {
                             if (c0 + c >= valid) e0 = 0.f;
                             if (c0 + c + 1 >= valid) e1 = 0.f;
-                        } else {
-                            e0 = exp2f(fmaf(__uint_as_float(r[c]), scale_l2, fmaf(-kLog2e, cs[c0 + c], neg_m)));
-                            e1 = exp2f(fmaf(__uint_as_float(r[c + 1]), scale_l2, fmaf(-kLog2e, cs[c0 + c + 1], neg_m)));
                         }
-                        lsum += e0 + e1;
+                        lsum2 = f2_add(lsum2, f2_pack(e0, e1));
                         pk[c >> 1] = pack_bf16_alu(e0, e1);
                     }
                     tmem_st16(s_t + (c0 >> 1), pk);
                 }
                 tmem_wait_st();
+                float lsum, lsum_hi;
+                f2_unpack(lsum2, lsum, lsum_hi);
+                lsum += lsum_hi;
                 if (!kDense) mbar_arrive(&bars->cl_empty[cslot]);
                 l_run += lsum;
                 ++my_tiles;
