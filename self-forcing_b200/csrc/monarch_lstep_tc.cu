@@ -460,21 +460,21 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 const uint64_t scale2 = f2_pack(scale_l2, scale_l2), nl2 = f2_pack(-kLog2e, -kLog2e);
                 float mx = -INFINITY;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kKT; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(s_t + c0, r);
+                for (int c0 = 0; c0 < kKT; c0 += 64) {
+                    uint32_t r[64];
+                    tmem_ld64(s_t + c0, r);
                     tmem_wait_ld();
                     if (kDense && !tail) {
                         // no bias: the maximum of the raw dot products (the scale is positive), two per instruction
 #pragma unroll
-                        for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+                        for (int c = 0; c < 64; c += 2) mx = max3(mx, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
                     } else if (kDense) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c)                         // keys past the end of the cache view
+                        for (int c = 0; c < 64; ++c)                         // keys past the end of the cache view
                             mx = fmaxf(mx, c0 + c < valid ? __uint_as_float(r[c]) : -INFINITY);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 32; c += 2) {                    // packed fp32 pairs: S * scale - log2(e) * cL
+                        for (int c = 0; c < 64; c += 2) {                    // packed fp32 pairs: S * scale - log2(e) * cL
                             const uint64_t bias2 = f2_mul(nl2, *reinterpret_cast<const uint64_t*>(&cs[c0 + c]));
                             float x0, x1;
                             f2_unpack(f2_fma(f2_pack(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, bias2), x0, x1);
