@@ -101,11 +101,18 @@ class KVCache:
             self._ref["local_end_index"].fill_(step.store_local_end)
 
     def _roll(self, roll) -> None:
+        """Shift ``count`` tokens left from ``src`` to ``dst`` (the eviction of causal_model.py:917-926).  The
+        ranges overlap, so the reference copies through a temporary; here the shift is done in place, in
+        stream order, in pieces no longer than the shift distance (a piece's source is then disjoint from its
+        destination, and a later piece only overwrites tokens an earlier piece has already read)."""
         dst, src, count = roll
-        if count <= 0:
+        if count <= 0 or src == dst:
             return
+        step = src - dst
         for t in (self.k, self.v):
-            t[:, dst:dst + count] = t[:, src:src + count].clone()     # ranges overlap: copy through a temporary
+            for off in range(0, count, step):
+                n = min(step, count - off)
+                t[:, dst + off:dst + off + n].copy_(t[:, src + off:src + off + n])
 
 
 @dataclass

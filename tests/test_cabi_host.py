@@ -157,3 +157,18 @@ def test_plan_cache_step_equals_oracle(sfb):
             g_end, l_end = b.store_global_end, b.store_local_end
             if window == -1 and chunk >= 7:
                 break
+
+
+def test_cache_roll_in_place_equals_copy_through_temporary(sfb):
+    """KVCache._roll shifts in place, piece by piece; the reference clones the source range first
+    (causal_model.py:917-926).  Same result for every overlap pattern."""
+    import torch
+    for dst, src, count in [(48, 192, 240), (0, 144, 288), (48, 96, 300), (5, 6, 100), (0, 300, 100), (7, 7, 50)]:
+        k = torch.arange(2 * 600 * 128, dtype=torch.float32).reshape(2, 600, 1, 128).to(torch.bfloat16)
+        v = k.clone() + 1
+        ref_k, ref_v = k.clone(), v.clone()
+        ref_k[:, dst:dst + count] = k[:, src:src + count].clone()
+        ref_v[:, dst:dst + count] = v[:, src:src + count].clone()
+        c = sfb.KVCache(k, v)
+        c._roll((dst, src, count))
+        assert torch.equal(c.k, ref_k) and torch.equal(c.v, ref_v), (dst, src, count)
