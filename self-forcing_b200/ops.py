@@ -18,6 +18,7 @@ from . import _lib
 
 _workspaces: Dict[Tuple[int, str], torch.Tensor] = {}
 _rope_tables: Dict[tuple, torch.Tensor] = {}
+_status_mirror: Dict[int, list] = {}
 
 
 # ------------------------------------------------------------------------------------- helpers
@@ -59,6 +60,43 @@ def _workspace(device: torch.device, nbytes: int, tag: str = "monarch") -> torch
         ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+_WATCH_EVERY = 32
+
+
+def _watch_status(ws: torch.Tensor) -> None:
+    """Keeps device-side failures loud without synchronising.  Every _WATCH_EVERY-th call on a GPU copies
+    the workspace's status word to pinned host memory on the call's stream (a small device-to-host copy
+    costs several microseconds of stream time, too much for every call); every call first looks at what
+    the last such copy delivered.  A kernel that gave up on a bounded wait sets the word, every later
+    launch on that workspace leaves a set word alone only until the next call clears it, so a persistent
+    fault is reported within _WATCH_EVERY calls and a transient one may pass unseen: the synchronous
+    check (SFM_CHECK_STATUS=1, or check_device_status()) is the strict form."""
+    key = ws.device.index if ws.device.index is not None else torch.cuda.current_device()
+    state = _status_mirror.get(key)
+    if state is None:
+        state = [torch.zeros(1, dtype=torch.int32).pin_memory(), 0]
+        _status_mirror[key] = state
+    host = state[0]
+    code = int(host[0])
+    if code != 0:
+        host[0] = 0
+        raise RuntimeError(f"an earlier Monarch attention call on this GPU recorded device status {code} "
+                           "(a kernel gave up on a bounded wait); its output is not valid")
+    state[1] += 1
+    if state[1] % _WATCH_EVERY == 0:
+        host.copy_(ws[:4].view(torch.int32), non_blocking=True)
+
+
+def check_device_status(device=None) -> None:
+    """Synchronous form: waits for the work queued on the current stream and raises if the last Monarch
+    attention call on ``device`` left a non-zero status word."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), "monarch")
+    ws = _workspaces.get(key)
+    if ws is not None:
+        _lib.check(_lib.load().sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
 
 
 def _rope_table_from_freqs(freqs: Optional[torch.Tensor], device: torch.device) -> torch.Tensor:
@@ -121,6 +159,8 @@ def _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale
     _lib.check(rc, "sfm_monarch_fwd")
     if os.environ.get("SFM_CHECK_STATUS") == "1":      # debugging aid: synchronises the stream
         _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
+    else:
+        _watch_status(ws)
     return out
 
 

@@ -558,3 +558,26 @@ def test_monarch_seeded_shape_sweep(sfb, cfg):
     torch.cuda.synchronize()
     check_close(got, ref, str(cfg))
     assert torch.equal(kg.cpu().float(), kc) and torch.equal(vg.cpu().float(), vc)
+
+
+@pytest.mark.gpu
+def test_status_watch_without_synchronising(sfb, monkeypatch):
+    """Without SFM_CHECK_STATUS the Python layer mirrors the device status word to pinned memory every few
+    calls and looks at the mirror on each call: healthy calls leave it at zero, a non-zero word left by a
+    (here simulated) failed call makes the next call raise, and check_device_status() is the synchronous form."""
+    from self_forcing_b200 import ops
+    monkeypatch.delenv("SFM_CHECK_STATUS", raising=False)
+    monkeypatch.setattr(ops, "_WATCH_EVERY", 2)
+    c = small_case(0, 1)
+    for _ in range(5):
+        z, _, _ = run_gpu_cache(sfb, c)
+    torch.cuda.synchronize()
+    dev = torch.cuda.current_device()
+    assert int(ops._status_mirror[dev][0][0]) == 0
+    ops.check_device_status()
+    ops._status_mirror[dev][0][0] = 31                   # what a softmax warp's timed-out wait would leave
+    with pytest.raises(RuntimeError, match="device status 31"):
+        run_gpu_cache(sfb, c)
+    z2, _, _ = run_gpu_cache(sfb, c)                     # the report clears the mirror
+    torch.cuda.synchronize()
+    assert torch.equal(z, z2)
