@@ -12,10 +12,11 @@
 //   cL = sum_l P ln P                    from the softmax registers
 // and streams aL, Y (bf16) and cL to the chunk's bridge.
 //
-// Warp roles (20 warps): 0 = TMA producer, 1 = issuer of the [aL | Y] GEMMs (owns the TMEM
-// allocation), 2 = issuer of the S GEMMs, 3 idle,
-// 4..7 and 8..11 = two softmax warpgroups that take even / odd steps (each owns one of the two
-// S/P buffers in TMEM), 12..15 and 16..19 = two epilogue warpgroups (aL half / Y half of the
+// Warp roles (19 warps): 0 = TMA producer, 1 = issuer of the [aL | Y] GEMMs (owns the TMEM
+// allocation), 2 = issuer of the S GEMMs,
+// 3..6 and 7..10 = two softmax warpgroups that take even / odd steps (each owns one of the two
+// S/P buffers in TMEM; a warp reaches TMEM lane quadrant warp % 4, and four consecutive warps cover
+// all four), 11..14 and 15..18 = two epilogue warpgroups (aL half / Y half of the
 // accumulator).  The S GEMM of step i+1 overlaps the softmax of step i; the output accumulator is
 // single buffered and handed back to the MMA warp as soon as both halves sit in registers.  Each
 // epilogue thread owns one bridge row and writes it straight from registers with 32-byte stores.  All roles run the same unit loop and meet
@@ -36,7 +37,7 @@ using namespace tc;
 namespace {
 
 constexpr int kStages = 5;            // K/V tile ring
-constexpr int kThreads = 640;
+constexpr int kThreads = 608;          // 19 warps: one more would lower the register ceiling from 104 to 96
 constexpr int kTileRows = 128;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128;   // O = [aL | Y], 256 columns
@@ -254,9 +255,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 }
             }
         }
-    } else if (warp >= 4 && warp < 12) {
+    } else if (warp >= 3 && warp < 11) {
         // ------------------------------------------------------------------ softmax warpgroups
-        const int wg = (warp - 4) >> 2;                 // 0: even steps / buffer 0, 1: odd steps / buffer 1
+        const int wg = (warp - 3) >> 2;                 // 0: even steps / buffer 0, 1: odd steps / buffer 1
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;               // tile row == TMEM lane
         const int gl = row / RG, j = row - gl * RG;
@@ -359,9 +360,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 if (lane == 0 && quad == 0) TRACE(2, g, 2);
             }
         }
-    } else if (warp >= 12) {
+    } else if (warp >= 11) {
         // ------------------------------------------------------------------ epilogue warpgroups
-        const int which = (warp - 12) >> 2;              // 0: aL (columns 0..127 of O), 1: Y (columns 128..255)
+        const int which = (warp - 11) >> 2;              // 0: aL (columns 0..127 of O), 1: Y (columns 128..255)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const uint32_t o_t = tmem + ((uint32_t)(quad * 32) << 16) + kColO + which * kHeadDim;
