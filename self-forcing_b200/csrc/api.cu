@@ -34,7 +34,7 @@ int make_plan(Plan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int 
     int rc = make_blocking(&pl->blk, f_tied, h_reduce, w_reduce, h, w);
     if (rc) return rc;
     const Blocking& blk = pl->blk;
-    if (blk.b2 > kB2Max) return SFM_ERR_UNSUPPORTED;
+    if (blk.b2 > kB2MaxTc) return SFM_ERR_UNSUPPORTED;
     if (n_q % blk.tied_tokens) return SFM_ERR_BAD_SHAPE;
     const int group_tokens = blk.b1 * blk.b2;
     if (n_kv % group_tokens) return SFM_ERR_BAD_SHAPE;
@@ -137,6 +137,8 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     // Tensor-core path: single pass (block-causal included, for block rows up to 128).  The iterative
     // variant runs on the mma.sync kernels.
     const bool use_tc = num_iters == 1 && (causal_groups == 0 || pl.blk.b1 <= 128);
+    // block columns above 64 exist on the tensor-core kernels only (single pass, block rows up to 128)
+    if (pl.blk.b2 > kB2Max && !(use_tc && pl.blk.b1 <= 128)) return SFM_ERR_UNSUPPORTED;
     // only the tensor-core column step knows how to scatter its rows
     if (os && os->world > 1 && !(use_tc && pl.blk.b1 <= 128)) return SFM_ERR_UNSUPPORTED;
     int num_sms = 148;
@@ -262,7 +264,7 @@ extern "C" const char* sfm_error_string(int code) {
         case SFM_OK: return "success";
         case SFM_ERR_NULL_POINTER: return "null pointer argument";
         case SFM_ERR_BAD_SHAPE: return "sizes inconsistent with the blocking";
-        case SFM_ERR_UNSUPPORTED: return "unsupported size (head_dim must be 128, block columns <= 64)";
+        case SFM_ERR_UNSUPPORTED: return "unsupported size (head_dim must be 128; block columns <= 128, and <= 64 for the iterative variant or block rows above 128)";
         case SFM_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
         case SFM_ERR_WORKSPACE: return "workspace too small";
         case SFM_ERR_NO_DEVICE: return "no sm_100 device";

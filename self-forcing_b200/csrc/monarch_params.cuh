@@ -51,7 +51,8 @@ struct MonarchParams {
 
 constexpr int kRWarps = 8;         // row-step CTA: 8 warps, one 16-row m-tile at a time each
 constexpr int kRMaxRows = 160;     // stacked (query group, column) rows per row-step CTA
-constexpr int kB2Max = 64;         // block columns supported (padded to a multiple of 16)
+constexpr int kB2Max = 64;         // block columns the mma.sync kernels support (padded to a multiple of 16)
+constexpr int kB2MaxTc = 128;      // block columns the tensor-core kernels support
 constexpr int kLWarps = 4;         // column-step CTA: 4 warps splitting each 128-key tile
 constexpr int kLTileKeys = 128;
 constexpr int kLQRows = 32;        // query rows (i) per column-step CTA

@@ -121,7 +121,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
     unsigned char* kv_s = q_s + kQBytes;
-    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + kStages * kStageBytes);
+    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + (N_S > 64 ? 2 * 2 * kStageBytes : kStages * kStageBytes));
 
 #ifdef SFM_TRACE
     __shared__ long long trace_s[8 * 32 * 4];
@@ -134,11 +134,17 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     const int b1 = blk.b1, b2 = blk.b2;
     const int RG = rp.rows_per_group;
     constexpr int kHalf = N_S * 128;                    // bytes of one 64-column half of a K or V tile
+    // Block columns above 64 (wide grids): 128-row K / V stages (two of them fit), S/P buffers and the
+    // accumulator move up in TMEM, and the softmax walks its row in 32-column chunks (see below).
+    constexpr bool kWide = N_S > 64;
+    constexpr int kStg = kWide ? 2 : kStages;
+    constexpr int kStgBytes = kWide ? 2 * kStageBytes : kStageBytes;
+    constexpr uint32_t cS1 = kWide ? 128u : kColS1, cO = kWide ? 256u : kColO;
 
     if (tid == 0) {
         mbar_init(&bars->q_full, 1);
         mbar_init(&bars->q_empty, 1);
-        for (int s = 0; s < kStages; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
+        for (int s = 0; s < kStg; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->s_full[s], 1); mbar_init(&bars->p_full[s], 128); }
         for (int s = 0; s < 2; ++s) mbar_init(&bars->sp_free[s], 1);
         mbar_init(&bars->o_full, 1);
@@ -177,11 +183,11 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     tma_load_4d(q_s + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full, 64, hd, tok, b);
                 }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
-                    const int s = g % kStages;
+                    const int s = g % kStg;
                     if (ABLATE(8)) continue;
-                    if (g >= kStages && !mbar_wait(&bars->kv_empty[s], ((g / kStages) - 1) & 1)) { fail(11); break; }
+                    if (g >= kStg && !mbar_wait(&bars->kv_empty[s], ((g / kStg) - 1) & 1)) { fail(11); break; }
                     const int tok = ((un.f_begin + i) * b1 + un.k) * b2;
-                    unsigned char* st = kv_s + s * kStageBytes;
+                    unsigned char* st = kv_s + s * kStgBytes;
                     TRACE(0, g, 0);
                     mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(4 * kHalf));
                     tma_load_4d(st, &tk, &bars->kv_full[s], 0, hd, tok, b);
@@ -207,12 +213,12 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 if (kCausal && un.n_it == 0) continue;
                 if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
-                    const int s = g % kStages;
-                    if (!ABLATE(8) && !mbar_wait(&bars->kv_full[s], (g / kStages) & 1)) { fail(21); ok = false; break; }
+                    const int s = g % kStg;
+                    if (!ABLATE(8) && !mbar_wait(&bars->kv_full[s], (g / kStg) & 1)) { fail(21); ok = false; break; }
                     if (g >= 2 && !mbar_wait(&bars->sp_free[g & 1], ((g >> 1) - 1) & 1)) { fail(25); ok = false; break; }
                     tc_fence_after();
-                    const uint64_t kd = k_desc0 + (uint64_t)((s * kStageBytes) >> 4);
-                    const uint32_t d = tmem + ((g & 1) ? kColS1 : kColS0);
+                    const uint64_t kd = k_desc0 + (uint64_t)((s * kStgBytes) >> 4);
+                    const uint32_t d = tmem + ((g & 1) ? cS1 : kColS0);
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const uint32_t q_off = ((ks >> 2) * (kTileRows * 128) + (ks & 3) * 32) >> 4;
@@ -242,12 +248,12 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     if (g > 0 && !mbar_wait(&bars->o_free, (g - 1) & 1)) { fail(23); ok = false; break; }
                     TRACE(1, g, 2);
                     tc_fence_after();
-                    const int s = g % kStages;
-                    const uint64_t bd = kv_desc_mn0 + (uint64_t)((s * kStageBytes) >> 4);
-                    const uint32_t p_t = tmem + ((g & 1) ? kColS1 : kColS0);
+                    const int s = g % kStg;
+                    const uint64_t bd = kv_desc_mn0 + (uint64_t)((s * kStgBytes) >> 4);
+                    const uint32_t p_t = tmem + ((g & 1) ? cS1 : kColS0);
 #pragma unroll
                     for (int kk = 0; kk < ksteps_pv; ++kk)
-                        mma_ts(tmem + kColO, p_t + kk * 8, bd + ((kk * 2048) >> 4), idesc_o, kk > 0);
+                        mma_ts(tmem + cO, p_t + kk * 8, bd + ((kk * 2048) >> 4), idesc_o, kk > 0);
                     mma_commit(&bars->o_full);
                     mma_commit(&bars->kv_empty[s]);
                     mma_commit(&bars->sp_free[g & 1]);
@@ -262,7 +268,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         const int row = quad * 32 + lane;               // tile row == TMEM lane
         const int gl = row / RG, j = row - gl * RG;
         const float scale_l2 = p.mult0 * kLog2e;
-        const uint32_t s_t = tmem + ((uint32_t)(quad * 32) << 16) + (wg ? kColS1 : kColS0);
+        const uint32_t s_t = tmem + ((uint32_t)(quad * 32) << 16) + (wg ? cS1 : kColS0);
         int g = 0;
         bool ok = true;
         for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
@@ -281,6 +287,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 tc_fence_after();
                 if (lane == 0 && quad == 0) TRACE(2, g, 1);
                 if (warp_active && !ABLATE(1)) {
+                    if constexpr (!kWide) {
                     uint32_t raw[N_S];
                     if constexpr (N_S == 64) {
                         tmem_ld32(s_t, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
@@ -354,6 +361,72 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                         p.cL[aj * p.n_keys_c + key] =
                             (!kCausal || un.f_begin + i < f_allowed) ? 0.6931471805599453f * ent * inv_z - __logf(z) : INFINITY;
                     }
+                    } else {
+                    // Wide rows: three passes over the row in 32-column chunks read back from TMEM (maximum;
+                    // sum and entropy; normalised P written over the S columns already consumed).
+                    auto load_chunk = [&](int c0, uint32_t (&r)[32]) {
+                        if (c0 + 32 <= N_S) {
+                            tmem_ld32(s_t + c0, r);
+                        } else {
+                            tmem_ld16(s_t + c0, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
+                        }
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (c0 + c >= b2) r[c] = 0xf149f2cau;          // -1e30, as above
+                    };
+                    float mx = -INFINITY;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < N_S; c0 += 32) {
+                        uint32_t r[32];
+                        load_chunk(c0, r);
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+                    }
+                    const float neg_m = -mx * scale_l2;
+                    const uint64_t scale2 = f2_pack(scale_l2, scale_l2), negm2 = f2_pack(neg_m, neg_m);
+                    uint64_t z2 = f2_pack(0.f, 0.f), ent2 = z2;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < N_S; c0 += 32) {
+                        uint32_t r[32];
+                        load_chunk(c0, r);
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            const uint64_t d2 = f2_fma(f2_pack(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, negm2);
+                            float d0, d1;
+                            f2_unpack(d2, d0, d1);
+                            const uint64_t e2 = f2_pack(exp2f(d0), exp2f(d1));
+                            z2 = f2_add(z2, e2);
+                            ent2 = f2_fma(e2, d2, ent2);
+                        }
+                    }
+                    float z, zh, ent, enth;
+                    f2_unpack(z2, z, zh);
+                    f2_unpack(ent2, ent, enth);
+                    z += zh;
+                    ent += enth;
+                    const float inv_z = 1.0f / z;
+                    const uint64_t invz2 = f2_pack(inv_z, inv_z);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < N_S; c0 += 32) {
+                        uint32_t r[32], pk[16];
+                        load_chunk(c0, r);
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            float d0, d1, p0, p1;
+                            f2_unpack(f2_fma(f2_pack(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, negm2), d0, d1);
+                            f2_unpack(f2_mul(f2_pack(exp2f(d0), exp2f(d1)), invz2), p0, p1);
+                            pk[c >> 1] = pack_bf16_alu(p0, p1);
+                        }
+                        tmem_st16(s_t + (c0 >> 1), pk);
+                    }
+                    tmem_wait_st();
+                    if (row_ok) {
+                        const int key = (un.f_begin + i) * b1 + un.k;
+                        p.cL[aj * p.n_keys_c + key] =
+                            (!kCausal || un.f_begin + i < f_allowed) ? 0.6931471805599453f * ent * inv_z - __logf(z) : INFINITY;
+                    }
+                    }
                 }
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[wg]);
@@ -365,7 +438,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         const int which = (warp - 11) >> 2;              // 0: aL (columns 0..127 of O), 1: Y (columns 128..255)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        const uint32_t o_t = tmem + ((uint32_t)(quad * 32) << 16) + kColO + which * kHeadDim;
+        const uint32_t o_t = tmem + ((uint32_t)(quad * 32) << 16) + cO + which * kHeadDim;
         int g = 0;
         bool ok = true;
         for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
@@ -452,10 +525,12 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v 
     rp.ablate = g_sfm_ablate;
 #endif
     dim3 grid(rp.n_units < num_sms ? rp.n_units : num_sms);
+    // wide blocks: two 64 KB K / V stages instead of five 32 KB ones
+    const int smem_bytes = n_s > 64 ? 1024 + kQBytes + 2 * 2 * kStageBytes + 256 : kSmemBytes;
     auto go = [&](auto kernel) -> int {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return (int)e;
-        kernel<<<grid, kThreads, kSmemBytes, s>>>(maps[0], maps[1], maps[2], rp);
+        kernel<<<grid, kThreads, smem_bytes, s>>>(maps[0], maps[1], maps[2], rp);
         return 0;
     };
     int rc;
@@ -465,6 +540,10 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v 
         case 32: rc = causal ? go(monarch_r_tc_kernel<32, true>) : go(monarch_r_tc_kernel<32, false>); break;
         case 48: rc = causal ? go(monarch_r_tc_kernel<48, true>) : go(monarch_r_tc_kernel<48, false>); break;
         case 64: rc = causal ? go(monarch_r_tc_kernel<64, true>) : go(monarch_r_tc_kernel<64, false>); break;
+        case 80: rc = causal ? go(monarch_r_tc_kernel<80, true>) : go(monarch_r_tc_kernel<80, false>); break;
+        case 96: rc = causal ? go(monarch_r_tc_kernel<96, true>) : go(monarch_r_tc_kernel<96, false>); break;
+        case 112: rc = causal ? go(monarch_r_tc_kernel<112, true>) : go(monarch_r_tc_kernel<112, false>); break;
+        case 128: rc = causal ? go(monarch_r_tc_kernel<128, true>) : go(monarch_r_tc_kernel<128, false>); break;
         default: return SFM_ERR_UNSUPPORTED;
     }
     if (rc) return rc;

@@ -533,6 +533,12 @@ def _sweep_configs():
         cached = rnd.randint(1, 5)
         out.append(dict(h=h, w=w, ft=ft, hr=hr, wr=wr, frames_q=frames_q, cached=cached, B=rnd.choice([1, 2]),
                         H=rnd.choice([1, 2, 3, 5]), T=rnd.choice([1, 1, 1, 2]), seed=rnd.randrange(1 << 30)))
+    # wide grids: block columns above 64 (two-stage K / V ring and the chunked row softmax of the row step)
+    for (h, w, hr, wr, ft, B, H, cached, fq) in [(4, 80, 1, 1, 1, 1, 2, 2, 3), (3, 128, 1, 1, 1, 2, 1, 1, 3),
+                                                 (6, 72, 2, 1, 1, 1, 3, 3, 6), (2, 104, 1, 1, 3, 1, 2, 2, 3),
+                                                 (4, 96, 4, 1, 1, 1, 1, 4, 3), (5, 66, 1, 1, 1, 1, 2, 1, 6)]:
+        out.append(dict(h=h, w=w, ft=ft, hr=hr, wr=wr, frames_q=fq, cached=cached, B=B, H=H, T=1,
+                        seed=rnd.randrange(1 << 30)))
     return out
 
 
