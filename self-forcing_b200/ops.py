@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 
-_workspaces: Dict[Tuple[int, str], torch.Tensor] = {}
+_workspaces: Dict[Tuple[int, int, str], torch.Tensor] = {}
 _rope_tables: Dict[tuple, torch.Tensor] = {}
 _status_mirror: Dict[int, list] = {}
 
@@ -54,7 +54,9 @@ def _batch_stride(t: torch.Tensor) -> int:
 
 
 def _workspace(device: torch.device, nbytes: int, tag: str = "monarch") -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), tag)
+    """Scratch for the row-step results, cached per (GPU, stream): calls queued on one stream run in order
+    and may share it, calls on different streams may overlap and must not."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), int(_stream().value or 0), tag)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
@@ -91,10 +93,10 @@ def _watch_status(ws: torch.Tensor) -> None:
 
 def check_device_status(device=None) -> None:
     """Synchronous form: waits for the work queued on the current stream and raises if the last Monarch
-    attention call on ``device`` left a non-zero status word."""
+    attention call queued on it (on ``device``) left a non-zero status word."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(), "monarch")
-    ws = _workspaces.get(key)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), int(_stream().value or 0), "monarch")
+    ws = _workspaces.get(key)                      # the workspace of the current stream
     if ws is not None:
         _lib.check(_lib.load().sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
 

@@ -587,3 +587,23 @@ def test_status_watch_without_synchronising(sfb, monkeypatch):
     z2, _, _ = run_gpu_cache(sfb, c)                     # the report clears the mirror
     torch.cuda.synchronize()
     assert torch.equal(z, z2)
+
+
+@pytest.mark.gpu
+def test_two_streams_use_separate_workspaces(sfb):
+    """Calls queued on different streams may overlap on the GPU: each stream gets its own scratch, and both
+    results equal the single-stream one."""
+    from self_forcing_b200 import ops
+    c = small_case(1, 1, H=3)
+    ref, _, _ = run_gpu_cache(sfb, c)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for s in (s1, s2, s1, s2):
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            outs.append(run_gpu_cache(sfb, c)[0])
+    torch.cuda.synchronize()
+    keys = {k for k in ops._workspaces if k[1] in (s1.cuda_stream, s2.cuda_stream)}
+    assert len(keys) == 2
+    for o in outs:
+        assert torch.equal(o, ref)
