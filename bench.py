@@ -239,6 +239,60 @@ def workload_config(args):
             "parallelism": f"dp{args.gpus} (independent chunks per GPU, no collective)"}
 
 
+def run_rollout(args, sfb, rank, world, device, barrier):
+    """The self-attention share of one Wan-1.3B video rollout on each GPU: 21 latent frames in 7 chunks of 3,
+    per chunk 4 denoising forwards plus the clean-context forward that refreshes the cache
+    (pipeline/causal_inference.py:203-245), per forward 30 layers, each layer one call of the layer path
+    (RMSNorm + RoPE + cache write in one kernel, then Monarch attention; dense attention for the first
+    chunk when --dense-init).  The projections' outputs are seeded random tensors shared by all layers;
+    every layer has its own KV cache (30 x 403 MB)."""
+    layers, chunks, forwards = 30, 7, 5
+    ft, hr, wr = BLOCKINGS[args.blocking]
+    cfg = sfb.LayerConfig(use_framewise=(ft == 1), h_reduce=hr, w_reduce=wr, use_dense_init=args.dense_init,
+                          max_attention_size=chunks * CHUNK)
+    g = torch.Generator(device="cpu").manual_seed(300 + rank)
+    mk = lambda: torch.randn(1, CHUNK, HEADS, HEAD_DIM, generator=g).to(torch.bfloat16).to(device)
+    qkv = [(mk(), mk(), mk()) for _ in range(3)]
+    wq = (torch.rand(HEADS * HEAD_DIM, generator=g) + 0.5).to(torch.bfloat16).to(device)
+    wk = (torch.rand(HEADS * HEAD_DIM, generator=g) + 0.5).to(torch.bfloat16).to(device)
+    caches = [sfb.KVCache.allocate(1, chunks * CHUNK, HEADS, device) for _ in range(layers)]
+
+    def video():
+        for c in caches:
+            c.reset()
+        out = None
+        for chunk in range(chunks):
+            for fwd in range(forwards):
+                q, k, v = qkv[(chunk + fwd) % 3]
+                for layer in range(layers):
+                    out = sfb.self_attention_kv(q, k, v, caches[layer], chunk * CHUNK, (CHUNK_FRAMES, H_GRID, W_GRID),
+                                                cfg, norm_q_weight=wq, norm_k_weight=wk)
+        return out
+
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 2))
+    ms = time_steps(video, steps, warmup, barrier) / steps
+    clocks = sampler.stop()
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    if rank == 0:
+        calls = layers * chunks * forwards
+        print(json.dumps({
+            "metric": "attention_rollout_latent_frames_per_s", "value": 21 * world / (ms * 1e-3),
+            "unit": "latent frames/s (self-attention layers of a Wan-1.3B rollout only)", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "ms_per_layer_call": ms / calls,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"self-attention of a 21-frame Wan-1.3B rollout: 7 chunks x 5 forwards x 30 layers = "
+                                   f"{calls} layer calls (RMSNorm + RoPE + cache write + {args.blocking} Monarch"
+                                   f"{', dense first chunk' if args.dense_init else ''}), 12 heads x 128, one video per GPU",
+                       "parallelism": f"dp{world}"},
+            "clocks": clocks}))
+
+
 def run_ulysses(args, sfb, rank, world, device, barrier):
     """Wan-14B self-attention layer (40 heads x 128) on one 3-frame chunk with the heads sharded over
     the ranks: every rank holds 4680/P tokens of q, k, v outside attention and 40/P heads (with their
@@ -343,6 +397,10 @@ def main():
     ap.add_argument("--ulysses", action="store_true",
                     help="time the Wan-14B attention layer (40 heads) with heads sharded over the GPUs "
                          "(token shards outside attention, two all-to-alls per layer) instead of the headline workload")
+    ap.add_argument("--rollout", action="store_true",
+                    help="time the self-attention share of a whole 21-frame Wan-1.3B rollout (7 chunks x 5 forwards x "
+                         "30 layers through the layer path) instead of the headline workload")
+    ap.add_argument("--dense-init", action="store_true", help="with --rollout: dense attention for the first chunk")
     ap.add_argument("--p2p", action="store_true",
                     help="with --ulysses: the kernels gather / scatter over peer memory instead of the two NCCL all-to-alls")
     args = ap.parse_args()
@@ -371,6 +429,12 @@ def main():
     import self_forcing_b200 as sfb
     from self_forcing_b200 import _lib
     lib = _lib.load()
+
+    if args.rollout:
+        run_rollout(args, sfb, rank, world, device, barrier)
+        if use_dist:
+            dist.destroy_process_group()
+        return
 
     if args.ulysses:
         run_ulysses(args, sfb, rank, world, device, barrier)
