@@ -460,13 +460,13 @@ def main():
     for _ in range(args.steps):
         step()
     torch.cuda.synchronize()
-    ms_cls = (C.c_float * 5)()
-    n_cls = (C.c_longlong * 5)()
-    _lib.check(lib.sfm_profile_read(ms_cls, n_cls, 5), "sfm_profile_read")
+    ms_cls = (C.c_float * 6)()
+    n_cls = (C.c_longlong * 6)()
+    _lib.check(lib.sfm_profile_read(ms_cls, n_cls, 6), "sfm_profile_read")
     lib.sfm_profile_enable(0)
-    cls_names = ["layout_rope_cache_write", "monarch_row_step", "monarch_col_step", "monarch_iter", "dense"]
+    cls_names = ["layout_rope_cache_write", "monarch_row_step", "monarch_col_step", "monarch_iter", "dense", "monarch_backward"]
     kernels = {cls_names[i]: {"launches_per_step": n_cls[i] / args.steps, "ms_per_step": ms_cls[i] / args.steps}
-               for i in range(5) if n_cls[i]}
+               for i in range(6) if n_cls[i]}
 
     # ---- end to end through the public API with host buffers --------------------------------
     qh, kh, vh = q.pin_memory(), kn.pin_memory(), vn.pin_memory()

@@ -251,9 +251,42 @@ int sfm_monarch_fwd_scatter(const void* q, int64_t q_batch_stride,
                             float sm_scale, size_t bridge_budget_bytes, void* stream);
 
 /*
+ * Backward of sfm_monarch_fwd (single pass): gradients of the attention output with respect to
+ * q and to the cached keys / values.
+ *   q        [B, n_q, H, D] bf16, natural token order, as given to sfm_monarch_fwd (batch stride
+ *            q_batch_stride elements)
+ *   k_cache, v_cache  [B, n_kv, H, D] bf16 in Monarch block order (batch stride kv_batch_stride)
+ *   dout     [B, n_q, H, D] bf16, contiguous, natural order: gradient of the output
+ *   dq       [B, n_q, H, D] fp32, contiguous, natural order: written (not accumulated)
+ *   dk, dv   [B, (kv_group_end - kv_group_begin) * b1 * b2, H, D] bf16, contiguous, Monarch block
+ *            order: gradients of the cached groups kv_group_begin .. kv_group_end - 1 (a group =
+ *            b1 * b2 tokens); the whole cache for 0 .. n_kv / (b1 * b2); may be null when the range
+ *            is empty.  The range is how grad_only_new_kv is expressed: the groups that the call
+ *            wrote.
+ *   workspace  sfm_monarch_bwd_workspace_bytes(...) bytes; the call is cut into slices of
+ *            (batch, head) pairs whose scratch stays under budget_bytes (0 = 2 GiB)
+ * The three kernels recompute the row step in fp32, so nothing has to be saved by the forward
+ * call; dq is accumulated without atomics (results are run-to-run identical).  Block rows and
+ * block columns up to 128.
+ * Replaces: _attention_with_cache.backward (wan/modules/monarch_attn.py:1325-1470) and its
+ * kernels (:403-596, 1034-1222).
+ */
+size_t sfm_monarch_bwd_workspace_bytes(int B, int H, int D, int n_q, int n_kv,
+                                       int f_tied, int h_reduce, int w_reduce, int h, int w,
+                                       size_t budget_bytes);
+int sfm_monarch_bwd(const void* q, int64_t q_batch_stride,
+                    const void* k_cache, const void* v_cache, int64_t kv_batch_stride,
+                    const void* dout, void* dq, void* dk, void* dv,
+                    void* workspace, size_t workspace_bytes,
+                    int B, int H, int D, int n_q, int n_kv,
+                    int f_tied, int h_reduce, int w_reduce, int h, int w,
+                    float sm_scale, int kv_group_begin, int kv_group_end,
+                    size_t budget_bytes, void* stream);
+
+/*
  * Launch accounting and optional per-kernel timing.  Kernel classes: 0 layout / RoPE /
  * cache write, 1 Monarch row step, 2 Monarch column step, 3 Monarch iteration update,
- * 4 dense attention (SFM_NUM_KERNEL_CLASSES of them).
+ * 4 dense attention, 5 Monarch backward (SFM_NUM_KERNEL_CLASSES of them).
  *   sfm_launch_count    kernels this library has launched in this process
  *   sfm_profile_enable  when on, each launch is bracketed by CUDA events on its stream
  *   sfm_profile_read    waits for the recorded events, returns per-class total milliseconds
@@ -261,7 +294,7 @@ int sfm_monarch_fwd_scatter(const void* q, int64_t q_batch_stride,
  * Replaces: the CUDA-event profiling of CausalInferencePipeline.inference(profile=True)
  * (pipeline/causal_inference.py:104-115, 247-281), at kernel granularity.
  */
-#define SFM_NUM_KERNEL_CLASSES 5
+#define SFM_NUM_KERNEL_CLASSES 6
 long long sfm_launch_count(void);
 int sfm_profile_enable(int on);
 int sfm_profile_read(float* ms, long long* launches, int n_classes);

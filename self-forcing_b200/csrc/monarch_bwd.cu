@@ -1,0 +1,615 @@
+// Backward of single-pass (T = 1) Monarch attention against a KV cache: dQ, dK, dV from dOut.
+//
+// Forward, per (batch, head), with q^ = sqrt(scale) Q and k^ = sqrt(scale) K:
+//   row step     unit (a, f, k, j):  z_l = q^[a,k,j] . k^[f,k,l],  R = softmax_l z,
+//                aL = sum_l R_l k^[f,k,l],  Y = sum_l R_l V[f,k,l],  cL = sum_l R_l ln R_l
+//   column step  slab (a, j), query row i, key n = (f, k):  s = q^[a,i,j] . aL_n - cL_n,
+//                P = softmax_n s,  out[a,i,j] = sum_n P_n Y_n
+// Backward, three launches per slice of (batch, head) pairs, all arithmetic in fp32:
+//   1. bwd_row_forward_kernel   recomputes aL, Y, cL into the scratch area (fp32)
+//   2. bwd_col_kernel           per slab: the softmax statistics, delta_i = sum_n P dP, then
+//                               ds = P (dP - delta), dq^_i = sum_n ds aL_n (stored to dQ),
+//                               daL_n = sum_i ds q^_i and dY_n = sum_i P dOut_i (written over aL and Y in
+//                               place, tile by tile), dcL_n = -sum_i ds
+//   3. bwd_row_kernel           per block row k, looping over the cached groups f: per unit
+//                               dR_l = daL.k^_l + dY.V_l + dcL (ln R_l + 1), dz = R (dR - sum R dR),
+//                               dQ[a,k,j] += scale sum_l dz_l K_l (this CTA owns those rows: no atomics),
+//                               dK[f,k,l] = sqrt(scale) sum_(a,j) (R_l daL + dz_l q^), dV[f,k,l] = sum_(a,j) R_l dY
+// The kernels are plain fp32 FMA code staged through shared memory: correct and deterministic, not yet on
+// the tensor cores.
+//
+// Stands in for _attention_with_cache.backward and its Triton kernels
+// (wan/modules/monarch_attn.py:403-596, 1034-1222, 1325-1470), including grad_only_new_kv
+// (dK / dV only for a range of cached groups).  Unlike that code it accumulates dQ without atomics and keeps
+// the intermediate gradients in fp32.
+#include <algorithm>
+
+#include "common.cuh"
+#include "profile.cuh"
+
+namespace sfm {
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int kD = kHeadDim;
+constexpr int kKs = kD + 2;        // bf16 row stride of a K / V tile in shared memory (65 words: conflict-free by row)
+constexpr int kFs = kD + 1;        // fp32 row stride of the column kernel's tiles
+constexpr int kTileN = 32;         // keys per tile of the column kernel
+constexpr int kRowBatch = 32;      // unit rows per batch of the row kernel
+
+// 32-bit words of one K or V tile in shared memory, rounded to 16 bytes
+__host__ __device__ inline int kv_tile_words(int b2) { return (b2 * (kKs / 2) + 3) & ~3; }
+
+struct BwdParams {
+    const bf16 *q, *k, *v, *dout;
+    float* dq;
+    bf16 *dk, *dv;
+    float *aL, *Y, *cL, *dcL;      // scratch; aL / Y hold daL / dY after the column kernel
+    int64_t q_bs, kv_bs;           // batch strides of q and of the cache, in elements
+    int H, A, F, b1, b2, n_keys, n_q;
+    int bh0;                       // first (batch, head) pair of this slice
+    int g0, g1;                    // cached groups whose dK / dV are wanted
+    float scale, rs;               // softmax scale and its square root
+    Blocking blk;
+};
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float wmax(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float2 bf2(uint32_t w) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+}
+
+// K or V rows [b2][128] bf16 of cached group f, block row k -> shared memory (row stride kKs).
+__device__ __forceinline__ void load_kv_tile(uint32_t* dst, const bf16* src_row0, int64_t tok_stride, int b2, int tid,
+                                             int nthr) {
+    for (int idx = tid; idx < b2 * 16; idx += nthr) {
+        const int l = idx >> 4, c = idx & 15;
+        const uint4 u = *reinterpret_cast<const uint4*>(src_row0 + (int64_t)l * tok_stride + c * 8);
+        uint32_t* d = dst + l * (kKs / 2) + c * 4;
+        d[0] = u.x; d[1] = u.y; d[2] = u.z; d[3] = u.w;
+    }
+}
+
+// 4 consecutive bf16 -> 4 floats
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = bf2(u.x), b = bf2(u.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// 1. forward recompute of the row step.  grid (n_keys, slice of batch*head), 256 threads; a warp per unit row.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bwd_row_forward_kernel(const BwdParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int b2 = p.b2, n = blockIdx.x, f = n / p.b1, k = n - f * p.b1;
+    const int bhl = blockIdx.y, bh = p.bh0 + bhl, b = bh / p.H, hd = bh - b * p.H;
+    uint32_t* Ks = reinterpret_cast<uint32_t*>(smem);
+    uint32_t* Vs = Ks + kv_tile_words(b2);
+    float* qrow = reinterpret_cast<float*>(Vs + kv_tile_words(b2));      // [8][128]
+    float* rrow = qrow + 8 * kD;                                       // [8][128]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tok = (int64_t)p.H * kD;
+    const int64_t kv_off = (int64_t)b * p.kv_bs + ((int64_t)n * b2) * tok + hd * kD;
+    load_kv_tile(Ks, p.k + kv_off, tok, b2, threadIdx.x, 256);
+    load_kv_tile(Vs, p.v + kv_off, tok, b2, threadIdx.x, 256);
+    __syncthreads();
+    float* qs = qrow + warp * kD;
+    float* rs_ = rrow + warp * kD;
+    for (int row = warp; row < p.A * b2; row += 8) {
+        const int a = row / b2, j = row - a * b2;
+        const bf16* qp = p.q + (int64_t)b * p.q_bs + (int64_t)(p.blk.row_token(a, k) + j) * tok + hd * kD;
+        const float4 q4 = ld4(qp + lane * 4);
+        __syncwarp();
+        qs[lane * 4 + 0] = q4.x * p.rs; qs[lane * 4 + 1] = q4.y * p.rs;
+        qs[lane * 4 + 2] = q4.z * p.rs; qs[lane * 4 + 3] = q4.w * p.rs;
+        __syncwarp();
+        float z[4], mx = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int l = lane + 32 * u;
+            z[u] = -INFINITY;
+            if (l < b2) {
+                const uint32_t* kr = Ks + l * (kKs / 2);
+                float acc = 0.f;
+#pragma unroll 8
+                for (int w = 0; w < kD / 2; ++w) {
+                    const float2 kk = bf2(kr[w]);
+                    acc = fmaf(qs[2 * w], kk.x, acc);
+                    acc = fmaf(qs[2 * w + 1], kk.y, acc);
+                }
+                z[u] = acc * p.rs;
+            }
+            mx = fmaxf(mx, z[u]);
+        }
+        mx = wmax(mx);
+        float e[4], sum = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { e[u] = (lane + 32 * u < b2) ? __expf(z[u] - mx) : 0.f; sum += e[u]; }
+        sum = wsum(sum);
+        const float lse = mx + __logf(sum), inv = 1.f / sum;
+        float cl = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int l = lane + 32 * u;
+            if (l < b2) {
+                const float r = e[u] * inv;
+                rs_[l] = r;
+                cl += r * (z[u] - lse);
+            }
+        }
+        cl = wsum(cl);
+        __syncwarp();
+        float aa[4] = {0.f, 0.f, 0.f, 0.f}, yy[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int l = 0; l < b2; ++l) {
+            const float r = rs_[l];
+            const float2 k0 = bf2(Ks[l * (kKs / 2) + lane]), k1 = bf2(Ks[l * (kKs / 2) + 32 + lane]);
+            const float2 v0 = bf2(Vs[l * (kKs / 2) + lane]), v1 = bf2(Vs[l * (kKs / 2) + 32 + lane]);
+            aa[0] = fmaf(r, k0.x, aa[0]); aa[1] = fmaf(r, k0.y, aa[1]);
+            aa[2] = fmaf(r, k1.x, aa[2]); aa[3] = fmaf(r, k1.y, aa[3]);
+            yy[0] = fmaf(r, v0.x, yy[0]); yy[1] = fmaf(r, v0.y, yy[1]);
+            yy[2] = fmaf(r, v1.x, yy[2]); yy[3] = fmaf(r, v1.y, yy[3]);
+        }
+        const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
+        const int64_t o = (slab * p.n_keys + n) * kD;
+        *reinterpret_cast<float2*>(p.aL + o + 2 * lane) = make_float2(aa[0] * p.rs, aa[1] * p.rs);
+        *reinterpret_cast<float2*>(p.aL + o + 64 + 2 * lane) = make_float2(aa[2] * p.rs, aa[3] * p.rs);
+        *reinterpret_cast<float2*>(p.Y + o + 2 * lane) = make_float2(yy[0], yy[1]);
+        *reinterpret_cast<float2*>(p.Y + o + 64 + 2 * lane) = make_float2(yy[2], yy[3]);
+        if (lane == 0) p.cL[slab * p.n_keys + n] = cl;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// 2. column step backward.  grid (A * b2, slice of batch*head), 256 threads.  T = query rows per warp
+//    (row i = warp + 8 t), so block rows up to 8 T.
+// ---------------------------------------------------------------------------------------------------------
+template <int T>
+__global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int kRows = 8 * T;
+    float* qs = reinterpret_cast<float*>(smem);        // [kRows][kFs]   q^ rows (zero beyond b1)
+    float* dos = qs + kRows * kFs;                     // [kRows][kFs]   dOut rows
+    float* aLs = dos + kRows * kFs;                    // [kTileN][kFs]
+    float* Ys = aLs + kTileN * kFs;                    // [kTileN][kFs]
+    float* sP = Ys + kTileN * kFs;                     // [kRows][kTileN + 1]
+    float* sDS = sP + kRows * (kTileN + 1);            // [kRows][kTileN + 1]
+    float* cls = sDS + kRows * (kTileN + 1);           // [kTileN]
+    const int b1 = p.b1, b2 = p.b2, a = blockIdx.x / b2, j = blockIdx.x - a * b2;
+    const int bhl = blockIdx.y, bh = p.bh0 + bhl, b = bh / p.H, hd = bh - b * p.H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int64_t tok = (int64_t)p.H * kD;
+    const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
+    float* g_aL = p.aL + slab * p.n_keys * kD;
+    float* g_Y = p.Y + slab * p.n_keys * kD;
+    const float* g_cL = p.cL + slab * p.n_keys;
+    float* g_dcL = p.dcL + slab * p.n_keys;
+
+    for (int idx = tid; idx < kRows * 32; idx += 256) {
+        const int i = idx >> 5, c = idx & 31;
+        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = q4;
+        if (i < b1) {
+            const int64_t t = p.blk.row_token(a, i) + j;
+            q4 = ld4(p.q + (int64_t)b * p.q_bs + t * tok + hd * kD + c * 4);
+            d4 = ld4(p.dout + ((int64_t)b * p.n_q + t) * tok + hd * kD + c * 4);
+        }
+        float* qd = qs + i * kFs + c * 4;
+        qd[0] = q4.x * p.rs; qd[1] = q4.y * p.rs; qd[2] = q4.z * p.rs; qd[3] = q4.w * p.rs;
+        float* dd = dos + i * kFs + c * 4;
+        dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+    }
+
+    float m[T], ls[T], delta[T], dq[T][4];
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        m[t] = -INFINITY; ls[t] = 0.f; delta[t] = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dq[t][u] = 0.f;
+    }
+
+    for (int pass = 0; pass < 3; ++pass) {
+        for (int t0 = 0; t0 < p.n_keys; t0 += kTileN) {
+            __syncthreads();                           // previous tile's readers are done (also covers qs / dos)
+            for (int idx = tid; idx < kTileN * 32; idx += 256) {
+                const int n = idx >> 5, c = idx & 31;
+                float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), y4 = a4;
+                if (t0 + n < p.n_keys) {
+                    a4 = *reinterpret_cast<const float4*>(g_aL + (int64_t)(t0 + n) * kD + c * 4);
+                    if (pass > 0) y4 = *reinterpret_cast<const float4*>(g_Y + (int64_t)(t0 + n) * kD + c * 4);
+                }
+                float* ad = aLs + n * kFs + c * 4;
+                ad[0] = a4.x; ad[1] = a4.y; ad[2] = a4.z; ad[3] = a4.w;
+                float* yd = Ys + n * kFs + c * 4;
+                yd[0] = y4.x; yd[1] = y4.y; yd[2] = y4.z; yd[3] = y4.w;
+            }
+            if (tid < kTileN) cls[tid] = (t0 + tid < p.n_keys) ? g_cL[t0 + tid] : 0.f;
+            __syncthreads();
+
+            // logits (and dP = dOut_i . Y_n) for key `lane`, rows warp + 8 t
+            const bool valid = t0 + lane < p.n_keys;
+            float s[T], dp[T];
+#pragma unroll
+            for (int t = 0; t < T; ++t) { s[t] = 0.f; dp[t] = 0.f; }
+            {
+                const float* ar = aLs + lane * kFs;
+                const float* yr = Ys + lane * kFs;
+                for (int d = 0; d < kD; ++d) {
+                    const float av = ar[d];
+                    const float yv = pass > 0 ? yr[d] : 0.f;
+#pragma unroll
+                    for (int t = 0; t < T; ++t) {
+                        s[t] = fmaf(qs[(warp + 8 * t) * kFs + d], av, s[t]);
+                        if (pass > 0) dp[t] = fmaf(dos[(warp + 8 * t) * kFs + d], yv, dp[t]);
+                    }
+                }
+            }
+            const float cl = cls[lane];
+#pragma unroll
+            for (int t = 0; t < T; ++t) s[t] = valid ? s[t] - cl : -INFINITY;
+
+            if (pass == 0) {
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const float mn = fmaxf(m[t], wmax(s[t]));
+                    const float e = valid ? __expf(s[t] - mn) : 0.f;
+                    ls[t] = ls[t] * __expf(m[t] - mn) + wsum(e);
+                    m[t] = mn;
+                }
+                continue;
+            }
+            if (pass == 1) {
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const float pr = valid ? __expf(s[t] - m[t]) : 0.f;      // m holds the log-sum-exp now
+                    delta[t] += wsum(pr * dp[t]);
+                }
+                continue;
+            }
+            // pass 2
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const float pr = valid ? __expf(s[t] - m[t]) : 0.f;
+                sP[(warp + 8 * t) * (kTileN + 1) + lane] = pr;
+                sDS[(warp + 8 * t) * (kTileN + 1) + lane] = pr * (dp[t] - delta[t]);
+            }
+            __syncthreads();
+            // dq^_i += sum_n ds[i][n] aL_n
+            for (int n = 0; n < kTileN; ++n) {
+                float av[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) av[u] = aLs[n * kFs + lane + 32 * u];
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const float ds = sDS[(warp + 8 * t) * (kTileN + 1) + n];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) dq[t][u] = fmaf(ds, av[u], dq[t][u]);
+                }
+            }
+            // daL_n = sum_i ds q^_i, dY_n = sum_i P dOut_i for keys warp + 8 v; written over aL / Y
+            {
+                float ga[4][4], gy[4][4];
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { ga[v][u] = 0.f; gy[v][u] = 0.f; }
+                for (int i = 0; i < b1; ++i) {
+                    float qv[4], dv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { qv[u] = qs[i * kFs + lane + 32 * u]; dv[u] = dos[i * kFs + lane + 32 * u]; }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const float ds = sDS[i * (kTileN + 1) + warp + 8 * v];
+                        const float pr = sP[i * (kTileN + 1) + warp + 8 * v];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            ga[v][u] = fmaf(ds, qv[u], ga[v][u]);
+                            gy[v][u] = fmaf(pr, dv[u], gy[v][u]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const int n = t0 + warp + 8 * v;
+                    if (n < p.n_keys) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            g_aL[(int64_t)n * kD + lane + 32 * u] = ga[v][u];
+                            g_Y[(int64_t)n * kD + lane + 32 * u] = gy[v][u];
+                        }
+                    }
+                }
+            }
+            if (tid < kTileN && t0 + tid < p.n_keys) {
+                float acc = 0.f;
+                for (int i = 0; i < b1; ++i) acc += sDS[i * (kTileN + 1) + tid];
+                g_dcL[t0 + tid] = -acc;
+            }
+        }
+        if (pass == 0) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) m[t] = m[t] + __logf(ls[t]);
+        }
+    }
+    // dQ = sqrt(scale) dq^ (the row kernel adds its share afterwards)
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        const int i = warp + 8 * t;
+        if (i < b1) {
+            float* o = p.dq + (((int64_t)b * p.n_q + p.blk.row_token(a, i) + j) * p.H + hd) * kD;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) o[lane + 32 * u] = dq[t][u] * p.rs;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// 3. row step backward.  grid (b1, slice of batch*head), 512 threads.  Per cached group f: phase 1, a warp per
+//    unit row (a, j), leaves R, dz, q^, daL, dY of a batch of rows in shared memory and adds the unit's
+//    share to dQ; phase 2, thread (d = tid % 128, l = tid / 128 + 4 t), accumulates dK[l][d], dV[l][d] over
+//    the batch.  LT = key columns per thread (block columns up to 4 LT).
+// ---------------------------------------------------------------------------------------------------------
+template <int LT>
+__global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int b2 = p.b2, k = blockIdx.x;
+    const int bhl = blockIdx.y, bh = p.bh0 + bhl, b = bh / p.H, hd = bh - b * p.H;
+    uint32_t* Ks = reinterpret_cast<uint32_t*>(smem);
+    uint32_t* Vs = Ks + kv_tile_words(b2);
+    float* qS = reinterpret_cast<float*>(Vs + kv_tile_words(b2));      // [kRowBatch][128]
+    float* daS = qS + kRowBatch * kD;
+    float* dyS = daS + kRowBatch * kD;
+    float* Rs = dyS + kRowBatch * kD;                                // [kRowBatch][b2]
+    float* dzs = Rs + kRowBatch * b2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int d_own = tid & 127, lq = tid >> 7;
+    const int64_t tok = (int64_t)p.H * kD;
+    const int n_rows = p.A * b2;
+
+    for (int f = 0; f < p.F; ++f) {
+        const int n = f * p.b1 + k;
+        const int64_t kv_off = (int64_t)b * p.kv_bs + ((int64_t)n * b2) * tok + hd * kD;
+        __syncthreads();                                             // the previous group's readers are done
+        load_kv_tile(Ks, p.k + kv_off, tok, b2, tid, 512);
+        load_kv_tile(Vs, p.v + kv_off, tok, b2, tid, 512);
+        float accK[LT], accV[LT];
+#pragma unroll
+        for (int t = 0; t < LT; ++t) { accK[t] = 0.f; accV[t] = 0.f; }
+        __syncthreads();
+
+        for (int r0 = 0; r0 < n_rows; r0 += kRowBatch) {
+            // ---- phase 1: rows r0 + warp and r0 + warp + 16
+            for (int slot = warp; slot < kRowBatch; slot += 16) {
+                const int row = r0 + slot;
+                if (row >= n_rows) break;
+                const int a = row / b2, j = row - a * b2;
+                const int64_t t_nat = p.blk.row_token(a, k) + j;
+                const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
+                const int64_t o = (slab * p.n_keys + n) * kD;
+                const float4 q4 = ld4(p.q + (int64_t)b * p.q_bs + t_nat * tok + hd * kD + lane * 4);
+                const float4 a4 = *reinterpret_cast<const float4*>(p.aL + o + lane * 4);
+                const float4 y4 = *reinterpret_cast<const float4*>(p.Y + o + lane * 4);
+                const float dcl = p.dcL[slab * p.n_keys + n];
+                float* qs = qS + slot * kD;
+                float* as = daS + slot * kD;
+                float* ys = dyS + slot * kD;
+                *reinterpret_cast<float4*>(qs + lane * 4) = make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
+                *reinterpret_cast<float4*>(as + lane * 4) = a4;
+                *reinterpret_cast<float4*>(ys + lane * 4) = y4;
+                __syncwarp();
+                float z[4], ga[4], mx = -INFINITY;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int l = lane + 32 * u;
+                    z[u] = -INFINITY; ga[u] = 0.f;
+                    if (l < b2) {
+                        const uint32_t* kr = Ks + l * (kKs / 2);
+                        const uint32_t* vr = Vs + l * (kKs / 2);
+                        float az = 0.f, aa = 0.f, ay = 0.f;
+#pragma unroll 4
+                        for (int w = 0; w < kD / 2; ++w) {
+                            const float2 kk = bf2(kr[w]), vv = bf2(vr[w]);
+                            az = fmaf(qs[2 * w], kk.x, az); az = fmaf(qs[2 * w + 1], kk.y, az);
+                            aa = fmaf(as[2 * w], kk.x, aa); aa = fmaf(as[2 * w + 1], kk.y, aa);
+                            ay = fmaf(ys[2 * w], vv.x, ay); ay = fmaf(ys[2 * w + 1], vv.y, ay);
+                        }
+                        z[u] = az * p.rs;
+                        ga[u] = aa * p.rs + ay;
+                    }
+                    mx = fmaxf(mx, z[u]);
+                }
+                mx = wmax(mx);
+                float e[4], sum = 0.f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { e[u] = (lane + 32 * u < b2) ? __expf(z[u] - mx) : 0.f; sum += e[u]; }
+                sum = wsum(sum);
+                const float lse = mx + __logf(sum), inv = 1.f / sum;
+                float r[4], dr[4], rdr = 0.f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    r[u] = e[u] * inv;
+                    dr[u] = (lane + 32 * u < b2) ? ga[u] + dcl * (z[u] - lse + 1.f) : 0.f;
+                    rdr += r[u] * dr[u];
+                }
+                rdr = wsum(rdr);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int l = lane + 32 * u;
+                    if (l < b2) { Rs[slot * b2 + l] = r[u]; dzs[slot * b2 + l] = r[u] * (dr[u] - rdr); }
+                }
+                __syncwarp();
+                float dq[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int l = 0; l < b2; ++l) {
+                    const float dz = dzs[slot * b2 + l];
+                    const float2 k0 = bf2(Ks[l * (kKs / 2) + lane]), k1 = bf2(Ks[l * (kKs / 2) + 32 + lane]);
+                    dq[0] = fmaf(dz, k0.x, dq[0]); dq[1] = fmaf(dz, k0.y, dq[1]);
+                    dq[2] = fmaf(dz, k1.x, dq[2]); dq[3] = fmaf(dz, k1.y, dq[3]);
+                }
+                float* g = p.dq + (((int64_t)b * p.n_q + t_nat) * p.H + hd) * kD;
+                float2 g0 = *reinterpret_cast<float2*>(g + 2 * lane), g1 = *reinterpret_cast<float2*>(g + 64 + 2 * lane);
+                g0.x += p.scale * dq[0]; g0.y += p.scale * dq[1];
+                g1.x += p.scale * dq[2]; g1.y += p.scale * dq[3];
+                *reinterpret_cast<float2*>(g + 2 * lane) = g0;
+                *reinterpret_cast<float2*>(g + 64 + 2 * lane) = g1;
+            }
+            __syncthreads();
+            // ---- phase 2
+            const int nb = min(kRowBatch, n_rows - r0);
+            for (int rr = 0; rr < nb; ++rr) {
+                const float qd = qS[rr * kD + d_own], ad = daS[rr * kD + d_own], yd = dyS[rr * kD + d_own];
+#pragma unroll
+                for (int t = 0; t < LT; ++t) {
+                    const int l = lq + 4 * t;
+                    if (l < b2) {
+                        const float rv = Rs[rr * b2 + l], dz = dzs[rr * b2 + l];
+                        accK[t] = fmaf(rv, ad, fmaf(dz, qd, accK[t]));
+                        accV[t] = fmaf(rv, yd, accV[t]);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        if (f >= p.g0 && f < p.g1) {
+            const int64_t base = (int64_t)b * (p.g1 - p.g0) * p.b1 * b2 + ((int64_t)(f - p.g0) * p.b1 + k) * b2;
+#pragma unroll
+            for (int t = 0; t < LT; ++t) {
+                const int l = lq + 4 * t;
+                if (l < b2) {
+                    const int64_t o = ((base + l) * p.H + hd) * kD + d_own;
+                    p.dk[o] = __float2bfloat16(accK[t] * p.rs);
+                    p.dv[o] = __float2bfloat16(accV[t]);
+                }
+            }
+        }
+    }
+}
+
+}  // namespace
+
+namespace {
+constexpr size_t kDefaultBwdBudget = (size_t)2 << 30;     // scratch per slice of (batch, head) pairs
+
+inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct BwdPlan {
+    Blocking blk;
+    int A, F, n_keys, nbh;
+    size_t off_aL, off_Y, off_cL, off_dcL, total;
+};
+
+int make_bwd_plan(BwdPlan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce, int h,
+                  int w, size_t budget) {
+    if (D != kHeadDim) return SFM_ERR_UNSUPPORTED;
+    if (B <= 0 || H <= 0 || n_q <= 0 || n_kv <= 0) return SFM_ERR_BAD_SHAPE;
+    if (int rc = make_blocking(&pl->blk, f_tied, h_reduce, w_reduce, h, w)) return rc;
+    const Blocking& blk = pl->blk;
+    if (blk.b1 > 128 || blk.b2 > 128) return SFM_ERR_UNSUPPORTED;
+    if (n_q % blk.tied_tokens) return SFM_ERR_BAD_SHAPE;
+    const int group = blk.b1 * blk.b2;
+    if (n_kv % group) return SFM_ERR_BAD_SHAPE;
+    pl->A = n_q / group;
+    pl->F = n_kv / group;
+    pl->n_keys = pl->F * blk.b1;
+    if (budget == 0) budget = kDefaultBwdBudget;
+    const size_t per_bh = (size_t)pl->A * blk.b2 * pl->n_keys * (2 * kHeadDim + 2) * sizeof(float);
+    pl->nbh = (int)std::max<size_t>(1, std::min<size_t>((size_t)B * H, budget / per_bh));
+    const size_t units = (size_t)pl->nbh * pl->A * blk.b2 * pl->n_keys;
+    size_t o = 0;
+    pl->off_aL = o; o = up256(o + units * kHeadDim * sizeof(float));
+    pl->off_Y = o; o = up256(o + units * kHeadDim * sizeof(float));
+    pl->off_cL = o; o = up256(o + units * sizeof(float));
+    pl->off_dcL = o; o = up256(o + units * sizeof(float));
+    pl->total = o;
+    return SFM_OK;
+}
+
+template <typename K>
+int opt_in_smem(K kernel, size_t bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess ? 0 : 1;
+}
+}  // namespace
+}  // namespace sfm
+
+using namespace sfm;
+
+extern "C" size_t sfm_monarch_bwd_workspace_bytes(int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce,
+                                                  int w_reduce, int h, int w, size_t budget_bytes) {
+    BwdPlan pl;
+    if (make_bwd_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, budget_bytes)) return 0;
+    return pl.total;
+}
+
+extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                               int64_t kv_batch_stride, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                               size_t workspace_bytes, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce,
+                               int w_reduce, int h, int w, float sm_scale, int kv_group_begin, int kv_group_end,
+                               size_t budget_bytes, void* stream) {
+    if (!q || !k_cache || !v_cache || !dout || !dq || !workspace) return SFM_ERR_NULL_POINTER;
+    BwdPlan pl;
+    if (int rc = make_bwd_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, budget_bytes)) return rc;
+    if (!(sm_scale > 0.f)) return SFM_ERR_BAD_SHAPE;
+    if (kv_group_begin < 0 || kv_group_end > pl.F || kv_group_begin > kv_group_end) return SFM_ERR_BAD_SHAPE;
+    if (kv_group_end > kv_group_begin && (!dk || !dv)) return SFM_ERR_NULL_POINTER;
+    if (workspace_bytes < pl.total) return SFM_ERR_WORKSPACE;
+    for (const void* ptr : {q, k_cache, v_cache, dout, (const void*)dq, (const void*)dk, (const void*)dv,
+                            (const void*)workspace})
+        if (reinterpret_cast<uintptr_t>(ptr) & 15) return SFM_ERR_ALIGNMENT;
+    if ((q_batch_stride & 7) || (kv_batch_stride & 7)) return SFM_ERR_ALIGNMENT;
+
+    const Blocking& blk = pl.blk;
+    BwdParams p{};
+    p.q = (const bf16*)q; p.k = (const bf16*)k_cache; p.v = (const bf16*)v_cache; p.dout = (const bf16*)dout;
+    p.dq = (float*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv;
+    unsigned char* ws = (unsigned char*)workspace;
+    p.aL = (float*)(ws + pl.off_aL); p.Y = (float*)(ws + pl.off_Y);
+    p.cL = (float*)(ws + pl.off_cL); p.dcL = (float*)(ws + pl.off_dcL);
+    p.q_bs = q_batch_stride; p.kv_bs = kv_batch_stride;
+    p.H = H; p.A = pl.A; p.F = pl.F; p.b1 = blk.b1; p.b2 = blk.b2; p.n_keys = pl.n_keys; p.n_q = n_q;
+    p.g0 = kv_group_begin; p.g1 = kv_group_end;
+    p.scale = sm_scale; p.rs = sqrtf(sm_scale);
+    p.blk = blk;
+
+    const int T = blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16);
+    const int LT = blk.b2 <= 64 ? 16 : 32;
+    const size_t smem_fwd = (size_t)2 * kv_tile_words(blk.b2) * 4 + 2 * 8 * kD * sizeof(float);
+    const size_t smem_col = ((size_t)2 * 8 * T * kFs + 2 * kTileN * kFs + 2 * 8 * T * (kTileN + 1) + kTileN) * sizeof(float);
+    const size_t smem_row = (size_t)2 * kv_tile_words(blk.b2) * 4 +
+                            ((size_t)3 * kRowBatch * kD + 2 * kRowBatch * blk.b2) * sizeof(float);
+    int bad = opt_in_smem(bwd_row_forward_kernel, smem_fwd);
+    bad |= T == 4 ? opt_in_smem(bwd_col_kernel<4>, smem_col)
+                  : (T == 8 ? opt_in_smem(bwd_col_kernel<8>, smem_col) : opt_in_smem(bwd_col_kernel<16>, smem_col));
+    bad |= LT == 16 ? opt_in_smem(bwd_row_kernel<16>, smem_row) : opt_in_smem(bwd_row_kernel<32>, smem_row);
+    if (bad) return SFM_ERR_UNSUPPORTED;
+
+    cudaStream_t s = (cudaStream_t)stream;
+    const int BH = B * H;
+    for (int bh0 = 0; bh0 < BH; bh0 += pl.nbh) {
+        const int nbh = std::min(pl.nbh, BH - bh0);
+        p.bh0 = bh0;
+        {
+            LaunchScope scope(kClsBackward, s);
+            bwd_row_forward_kernel<<<dim3(pl.n_keys, nbh), 256, smem_fwd, s>>>(p);
+        }
+        {
+            LaunchScope scope(kClsBackward, s);
+            const dim3 grid(pl.A * blk.b2, nbh);
+            if (T == 4) bwd_col_kernel<4><<<grid, 256, smem_col, s>>>(p);
+            else if (T == 8) bwd_col_kernel<8><<<grid, 256, smem_col, s>>>(p);
+            else bwd_col_kernel<16><<<grid, 256, smem_col, s>>>(p);
+        }
+        {
+            LaunchScope scope(kClsBackward, s);
+            const dim3 grid(blk.b1, nbh);
+            if (LT == 16) bwd_row_kernel<16><<<grid, 512, smem_row, s>>>(p);
+            else bwd_row_kernel<32><<<grid, 512, smem_row, s>>>(p);
+        }
+    }
+    return cudaGetLastError() == cudaSuccess ? SFM_OK : SFM_ERR_UNSUPPORTED;
+}

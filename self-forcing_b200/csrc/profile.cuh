@@ -4,7 +4,7 @@
 
 namespace sfm {
 
-enum KernelClass { kClsLayout = 0, kClsRStep = 1, kClsLStep = 2, kClsLIter = 3, kClsDense = 4, kNumClasses = 5 };
+enum KernelClass { kClsLayout = 0, kClsRStep = 1, kClsLStep = 2, kClsLIter = 3, kClsDense = 4, kClsBackward = 5, kNumClasses = 6 };
 
 // Counts one launch of `cls`; when profiling is enabled also brackets the launch with events.
 struct LaunchScope {

@@ -166,15 +166,100 @@ def _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale
     return out
 
 
+def monarch_attn_with_kv_cache_backward(q, k_cache, v_cache, grad_out, f_tied, h_reduce, w_reduce, h, w, sm_scale=None,
+                                        kv_groups: Optional[Tuple[int, int]] = None, budget_bytes: int = 0):
+    """Gradients of ``monarch_attn_with_kv_cache`` (single pass) for a gradient ``grad_out`` of its output.
+
+    q, grad_out: [B, n_q, H, 128] bf16, natural token order; k_cache / v_cache: the cache view the forward
+    call attended, [B, n_kv, H, 128] bf16 in Monarch order.  ``kv_groups`` = (begin, end) limits dK / dV to
+    those cached groups (one group = b1 * b2 tokens, a frame for the framewise blocking); None = all.
+    Returns (dq fp32 [B, n_q, H, 128] natural order, dk, dv bf16 [B, groups * b1 * b2, H, 128] Monarch
+    order).  The call runs in slices of (batch, head) pairs whose fp32 scratch stays under ``budget_bytes``
+    (0 = 2 GiB).  Stands in for _attention_with_cache.backward (monarch_attn.py:1325-1470)."""
+    for t, name in ((q, "q"), (grad_out, "grad_out")):
+        _require(t, name)
+    _cache_view_ok(k_cache, "k_cache")
+    _cache_view_ok(v_cache, "v_cache")
+    if k_cache.stride() != v_cache.stride() or k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must share shape and strides")
+    if grad_out.shape != q.shape:
+        raise ValueError("grad_out must have q's shape")
+    B, n_q, H, D = q.shape
+    n_kv = k_cache.shape[1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    q = _as_token_major(q)
+    grad_out = grad_out.contiguous()
+    lib = _lib.load()
+    nbytes = lib.sfm_monarch_bwd_workspace_bytes(B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, budget_bytes)
+    ws = _workspace(q.device, max(int(nbytes), 256), "monarch_bwd")
+    group = (f_tied * h * w) // (h_reduce * w_reduce)
+    g0, g1 = (0, n_kv // group) if kv_groups is None else (int(kv_groups[0]), int(kv_groups[1]))
+    dq = torch.empty((B, n_q, H, D), dtype=torch.float32, device=q.device)
+    dk = torch.empty((B, max(g1 - g0, 0) * group, H, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty_like(dk)
+    rc = lib.sfm_monarch_bwd(_ptr(q), _batch_stride(q), _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache),
+                             _ptr(grad_out), _ptr(dq), _ptr(dk) if dk.numel() else None,
+                             _ptr(dv) if dv.numel() else None, _ptr(ws), ws.numel(), B, H, D, n_q, n_kv, f_tied,
+                             h_reduce, w_reduce, h, w, float(sm_scale), g0, g1, budget_bytes, _stream())
+    _lib.check(rc, "sfm_monarch_bwd")
+    return dq, dk, dv
+
+
+class _MonarchWithKVCacheFn(torch.autograd.Function):
+    """Cache write + Monarch attention with the backward kernels behind it.  Differentiable inputs: q,
+    new_k, new_v (natural order) and, unless grad_only_new_kv, the cache tensors."""
+
+    @staticmethod
+    def forward(ctx, q, new_k, new_v, k_cache, v_cache, start_idx, end_idx, blocking, sm_scale, grad_only_new_kv):
+        f_tied, h_reduce, w_reduce, h, w = blocking
+        out = monarch_attn_with_kv_cache(q.detach(), k_cache.detach(), v_cache.detach(), new_k.detach(), new_v.detach(),
+                                         start_idx, end_idx, f_tied, h_reduce, w_reduce, h, w, sm_scale, 1,
+                                         _no_grad=True)
+        ctx.save_for_backward(q, k_cache, v_cache)
+        ctx.args = (int(start_idx), int(end_idx), blocking, sm_scale, bool(grad_only_new_kv))
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k_cache, v_cache = ctx.saved_tensors
+        start, end, blocking, sm_scale, only_new = ctx.args
+        f_tied, h_reduce, w_reduce, h, w = blocking
+        group = (f_tied * h * w) // (h_reduce * w_reduce)
+        n_kv = k_cache.shape[1]
+        want_cache = not only_new and (ctx.needs_input_grad[3] or ctx.needs_input_grad[4])
+        g0, g1 = (0, n_kv // group) if want_cache else (start // group, -(-end // group))
+        dq, dk, dv = monarch_attn_with_kv_cache_backward(q, k_cache, v_cache, grad_out.to(q.dtype), f_tied, h_reduce,
+                                                         w_reduce, h, w, sm_scale, (g0, g1))
+        lo = start - g0 * group
+        nat2mon, _ = build_maps(end - start, f_tied, h_reduce, w_reduce, h, w)
+        idx = torch.from_numpy(nat2mon.astype(np.int64)).to(q.device)
+        d_new_k = dk[:, lo:lo + end - start].index_select(1, idx)
+        d_new_v = dv[:, lo:lo + end - start].index_select(1, idx)
+        d_kc = d_vc = None
+        if want_cache:                                  # the written slots do not depend on the cache's old content
+            d_kc, d_vc = dk.clone(), dv.clone()
+            d_kc[:, start:end] = 0
+            d_vc[:, start:end] = 0
+        return dq, d_new_k, d_new_v, d_kc, d_vc, None, None, None, None, None
+
+
 # ------------------------------------------------------------------------------------- public
 def monarch_attn_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end_idx, f_tied, h_reduce, w_reduce,
-                               h, w, sm_scale=None, num_iters=1, grad_only_new_kv=False):
+                               h, w, sm_scale=None, num_iters=1, grad_only_new_kv=False, _no_grad=False):
     """Same contract as the reference's monarch_attn_with_kv_cache (monarch_attn.py:1778-1796):
     new_k / new_v are written, in Monarch block order, into k_cache / v_cache[:, start_idx:end_idx]
-    IN PLACE, then q attends the whole cache view.  Forward only (grad_only_new_kv is accepted
-    and ignored).  q, new_k, new_v: [B, n, H, 128] bf16 (already rotated); caches [B, n_kv, H, 128]
-    bf16, possibly a [:, :n_kv] view of a longer buffer.  Returns [B, n_q, H, 128]."""
-    del grad_only_new_kv
+    IN PLACE, then q attends the whole cache view.  q, new_k, new_v: [B, n, H, 128] bf16 (already
+    rotated); caches [B, n_kv, H, 128] bf16, possibly a [:, :n_kv] view of a longer buffer.  Returns
+    [B, n_q, H, 128].  When autograd is recording and an input requires a gradient the call goes
+    through an autograd function whose backward runs the backward kernels (single pass only);
+    grad_only_new_kv then limits dK / dV to the slots this call wrote."""
+    if (not _no_grad and torch.is_grad_enabled()
+            and any(t.requires_grad for t in (q, new_k, new_v, k_cache, v_cache))):
+        if num_iters != 1:
+            raise NotImplementedError("the backward pass exists for num_iters == 1 only")
+        return _MonarchWithKVCacheFn.apply(q, new_k, new_v, k_cache, v_cache, start_idx, end_idx,
+                                           (f_tied, h_reduce, w_reduce, h, w), sm_scale, grad_only_new_kv)
     for t, name in ((q, "q"), (new_k, "new_k"), (new_v, "new_v")):
         _require(t, name)
     _cache_view_ok(k_cache, "k_cache")

@@ -1,0 +1,162 @@
+"""GPU parity tests of the Monarch attention backward kernels (through the C ABI) against autograd
+through the CPU oracle's forward in fp32 on the same bf16-rounded inputs.
+
+Tolerances: dq comes back in fp32 from fp32 arithmetic: relative L2 <= 2e-3; dk / dv are rounded to bf16 once:
+relative L2 <= 1e-2 and max-abs <= 2e-2 of the largest reference magnitude (the forward's acceptance rule,
+scaled to the gradient's range).
+"""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import monarch_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def sfb():
+    import self_forcing_b200
+    assert torch.cuda.is_available()
+    return self_forcing_b200
+
+
+def bf(x):
+    return x.to(torch.bfloat16)
+
+
+def grad_close(got, ref, rel_tol, what):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    assert torch.isfinite(got).all(), f"{what}: non-finite"
+    scale = ref.abs().max().clamp_min(1e-30).item()
+    err = (got - ref).abs().max().item() / scale
+    rel = ((got - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+    assert rel <= rel_tol and err <= 2e-2, f"{what}: rel-L2 {rel:.3e} max-abs/scale {err:.3e}"
+
+
+def make_case(blocking, frames_q, groups_cached, B, H, seed):
+    """Cache of `groups_cached` tied frame sets, the last `frames_q` of them written by this call."""
+    ft, hr, wr, h, w = blocking
+    rng = np.random.default_rng(seed)
+    tied = ft * h * w
+    n_q, n_kv = frames_q * tied, groups_cached * tied
+    mk = lambda *s: bf(cases.randn(rng, *s))
+    return dict(blocking=blocking, q=mk(B, n_q, H, 128), nk=mk(B, n_q, H, 128), nv=mk(B, n_q, H, 128),
+                kbuf=mk(B, n_kv + tied, H, 128), vbuf=mk(B, n_kv + tied, H, 128), g=mk(B, n_q, H, 128),
+                start=n_kv - n_q, end=n_kv, n_kv=n_kv, sm_scale=128 ** -0.5)
+
+
+def oracle_grads(c):
+    """Autograd through the oracle: gradients w.r.t. q, the cache content (Monarch order; zero where this call
+    wrote) and new_k / new_v (natural order)."""
+    q = c["q"].float().requires_grad_()
+    nk, nv = c["nk"].float().requires_grad_(), c["nv"].float().requires_grad_()
+    kb, vb = c["kbuf"].float().requires_grad_(), c["vbuf"].float().requires_grad_()
+    kc, vc = kb.clone(), vb.clone()
+    z = orc.monarch_attn_with_kv_cache(q, kc[:, :c["n_kv"]], vc[:, :c["n_kv"]], nk, nv, c["start"], c["end"],
+                                       *c["blocking"], sm_scale=c["sm_scale"])
+    (z * c["g"].float()).sum().backward()
+    return dict(q=q.grad, nk=nk.grad, nv=nv.grad, kc=kb.grad[:, :c["n_kv"]], vc=vb.grad[:, :c["n_kv"]], z=z.detach())
+
+
+def gpu_cache(sfb, c):
+    dev = "cuda"
+    kc, vc = c["kbuf"].to(dev).clone(), c["vbuf"].to(dev).clone()
+    kv, vv = kc[:, :c["n_kv"]], vc[:, :c["n_kv"]]
+    with torch.no_grad():
+        z = sfb.monarch_attn_with_kv_cache(c["q"].to(dev), kv, vv, c["nk"].to(dev), c["nv"].to(dev), c["start"], c["end"],
+                                           *c["blocking"], sm_scale=c["sm_scale"])
+    return z, kv, vv
+
+
+def direct_check(sfb, c, ref, budget=0):
+    _, kv, vv = gpu_cache(sfb, c)
+    dq, dk, dv = sfb.monarch_attn_with_kv_cache_backward(c["q"].cuda(), kv, vv, c["g"].cuda(), *c["blocking"],
+                                                         sm_scale=c["sm_scale"], budget_bytes=budget)
+    torch.cuda.synchronize()
+    assert dq.dtype == torch.float32
+    grad_close(dq, ref["q"], 2e-3, "dq")
+    # reference cache gradients are zero in the written slots; the kernels return the gradient w.r.t. the cache
+    # CONTENT there, which is the new keys' gradient in Monarch order
+    ft, hr, wr, h, w = c["blocking"]
+    full_k, full_v = ref["kc"].clone(), ref["vc"].clone()
+    full_k[:, c["start"]:c["end"]] = orc.to_monarch_order(ref["nk"], ft, hr, wr, h, w).reshape(full_k[:, c["start"]:c["end"]].shape)
+    full_v[:, c["start"]:c["end"]] = orc.to_monarch_order(ref["nv"], ft, hr, wr, h, w).reshape(full_v[:, c["start"]:c["end"]].shape)
+    grad_close(dk, full_k, 1e-2, "dk")
+    grad_close(dv, full_v, 1e-2, "dv")
+    return dq, dk, dv
+
+
+@pytest.mark.parametrize("ci", range(len(cases.SMALL_BLOCKINGS)))
+def test_backward_small_blockings(sfb, ci):
+    _, ft, hr, wr, h, w = cases.SMALL_BLOCKINGS[ci]
+    c = make_case((ft, hr, wr, h, w), frames_q=2 if ft == 1 else 1, groups_cached=4 if ft == 1 else 2, B=2, H=2,
+                  seed=8100 + ci)
+    direct_check(sfb, c, oracle_grads(c))
+
+
+@pytest.mark.parametrize("blocking,frames_q,cached", [((1, 1, 1, 30, 52), 1, 2), ((3, 1, 1, 30, 52), 1, 1),
+                                                      ((1, 2, 1, 30, 52), 1, 2), ((1, 2, 4, 30, 52), 1, 2),
+                                                      ((1, 1, 1, 45, 80), 1, 2), ((1, 1, 2, 8, 132), 2, 3)],
+                         ids=["framewise", "tied3frame", "reduce2xh", "reduce4xw2xh", "wide45x80", "b2_66"])
+def test_backward_real_block_sizes(sfb, blocking, frames_q, cached):
+    """Block rows 30 / 90 / 15 / 45 (all three row-per-warp instantiations of the column kernel), block columns
+    52 / 13 (odd) / 80 / 66 (both instantiations of the row kernel)."""
+    c = make_case(blocking, frames_q, cached, B=1, H=2, seed=8200 + blocking[3] + blocking[0])
+    direct_check(sfb, c, oracle_grads(c))
+
+
+def test_backward_is_deterministic_and_slicing_is_invisible(sfb):
+    c = make_case((1, 1, 1, 6, 8), 2, 4, B=2, H=3, seed=8300)
+    ref = oracle_grads(c)
+    a = direct_check(sfb, c, ref)
+    b = direct_check(sfb, c, ref)
+    one_pair = 2 * 8 * (4 * 6) * (2 * 128 + 2) * 4          # scratch of one (batch, head) pair: A b2 n_keys (2 D + 2) floats
+    s = direct_check(sfb, c, ref, budget=2 * one_pair)      # three slices of two pairs
+    for x, y, z in zip(a, b, s):
+        assert torch.equal(x, y) and torch.equal(x, z)
+
+
+def test_backward_group_range(sfb):
+    """grad_only_new_kv at the C ABI: dK / dV of a range of groups equal that slice of the full result; dq does
+    not depend on the range."""
+    c = make_case((1, 1, 1, 6, 8), 2, 5, B=1, H=2, seed=8400)
+    _, kv, vv = gpu_cache(sfb, c)
+    args = (c["q"].cuda(), kv, vv, c["g"].cuda(), *c["blocking"])
+    dq, dk, dv = sfb.monarch_attn_with_kv_cache_backward(*args, sm_scale=c["sm_scale"])
+    dq2, dk2, dv2 = sfb.monarch_attn_with_kv_cache_backward(*args, sm_scale=c["sm_scale"], kv_groups=(3, 5))
+    dq3, dk3, dv3 = sfb.monarch_attn_with_kv_cache_backward(*args, sm_scale=c["sm_scale"], kv_groups=(2, 2))
+    assert torch.equal(dq, dq2) and torch.equal(dq, dq3)
+    assert torch.equal(dk[:, 3 * 48:5 * 48], dk2) and torch.equal(dv[:, 3 * 48:5 * 48], dv2)
+    assert dk3.shape[1] == 0 and dv3.shape[1] == 0
+
+
+@pytest.mark.parametrize("only_new", [False, True])
+def test_autograd_function(sfb, only_new):
+    """monarch_attn_with_kv_cache under autograd: same forward result and cache content as without it;
+    gradients of q, new_k, new_v (natural order) and of the cache (zero where the call wrote; absent with
+    grad_only_new_kv)."""
+    c = make_case((1, 2, 1, 6, 8), 2, 4, B=2, H=2, seed=8500)
+    ref = oracle_grads(c)
+    z0, kv0, _ = gpu_cache(sfb, c)
+    dev = "cuda"
+    q = c["q"].to(dev).requires_grad_()
+    nk, nv = c["nk"].to(dev).requires_grad_(), c["nv"].to(dev).requires_grad_()
+    kv = c["kbuf"].to(dev).clone()[:, :c["n_kv"]].requires_grad_(not only_new)
+    vv = c["vbuf"].to(dev).clone()[:, :c["n_kv"]].requires_grad_(not only_new)
+    z = sfb.monarch_attn_with_kv_cache(q, kv, vv, nk, nv, c["start"], c["end"], *c["blocking"], sm_scale=c["sm_scale"],
+                                       grad_only_new_kv=only_new)
+    assert torch.equal(z, z0) and torch.equal(kv.detach(), kv0)
+    (z.float() * c["g"].to(dev).float()).sum().backward()
+    torch.cuda.synchronize()
+    grad_close(q.grad, ref["q"], 1e-2, "q.grad")
+    grad_close(nk.grad, ref["nk"], 1e-2, "new_k.grad")
+    grad_close(nv.grad, ref["nv"], 1e-2, "new_v.grad")
+    if only_new:
+        assert kv.grad is None and vv.grad is None
+    else:
+        grad_close(kv.grad, ref["kc"], 1e-2, "k_cache.grad")
+        grad_close(vv.grad, ref["vc"], 1e-2, "v_cache.grad")
+        assert not kv.grad[:, c["start"]:c["end"]].any()
