@@ -293,6 +293,42 @@ def run_rollout(args, sfb, rank, world, device, barrier):
             "clocks": clocks}))
 
 
+def run_backward(args, sfb, rank, world, device, barrier):
+    """Forward + backward of the Monarch attention op at the headline shape (one 3-frame chunk against k cached
+    chunks, 12 heads): the call a training rollout makes per layer (gradients of q and of the chunk's own keys
+    and values, as with grad_only_new_kv)."""
+    ft, hr, wr = BLOCKINGS[args.blocking]
+    n_kv = args.k * CHUNK
+    g = torch.Generator(device="cpu").manual_seed(400 + rank)
+    mk = lambda n: torch.randn(1, n, HEADS, HEAD_DIM, generator=g).to(torch.bfloat16).to(device)
+    q, kc, vc, do = mk(CHUNK), mk(n_kv), mk(n_kv), mk(CHUNK)
+    group = ft * H_GRID * W_GRID // (hr * wr)
+    groups = (n_kv // group - CHUNK // group, n_kv // group)
+    fwd = lambda: sfb.ops.monarch_attention_on_cache(q, kc, vc, ft, hr, wr, H_GRID, W_GRID)
+    bwd = lambda: sfb.monarch_attn_with_kv_cache_backward(q, kc, vc, do, ft, hr, wr, H_GRID, W_GRID, kv_groups=groups)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    ms_f = time_steps(fwd, args.steps, args.warmup, barrier) / args.steps
+    ms_b = time_steps(bwd, args.steps, args.warmup, barrier) / args.steps
+    clocks = sampler.stop()
+    t = torch.tensor([ms_f, ms_b], device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_f, ms_b = t.tolist()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "attention_fwd_bwd_latent_frames_per_s", "value": CHUNK_FRAMES * world / ((ms_f + ms_b) * 1e-3),
+            "unit": "latent frames/s (forward + backward of the attention op)", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_f + ms_b, "forward_ms": ms_f, "backward_ms": ms_b,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 in, fp32 arithmetic in the backward",
+            "data": "synthetic",
+            "config": {"workload": f"{args.blocking} Monarch attention forward + backward, one 3-frame chunk vs k={args.k} "
+                                   f"cached chunks ({n_kv} tokens), 12 heads x 128, dK/dV of the chunk's own groups",
+                       "parallelism": f"dp{world}"},
+            "clocks": clocks}))
+
+
 def run_ulysses(args, sfb, rank, world, device, barrier):
     """Wan-14B self-attention layer (40 heads x 128) on one 3-frame chunk with the heads sharded over
     the ranks: every rank holds 4680/P tokens of q, k, v outside attention and 40/P heads (with their
@@ -400,6 +436,8 @@ def main():
     ap.add_argument("--rollout", action="store_true",
                     help="time the self-attention share of a whole 21-frame Wan-1.3B rollout (7 chunks x 5 forwards x "
                          "30 layers through the layer path) instead of the headline workload")
+    ap.add_argument("--backward", action="store_true",
+                    help="time forward + backward of the attention op at the headline shape instead of the headline workload")
     ap.add_argument("--dense-init", action="store_true", help="with --rollout: dense attention for the first chunk")
     ap.add_argument("--p2p", action="store_true",
                     help="with --ulysses: the kernels gather / scatter over peer memory instead of the two NCCL all-to-alls")
@@ -432,6 +470,12 @@ def main():
 
     if args.rollout:
         run_rollout(args, sfb, rank, world, device, barrier)
+        if use_dist:
+            dist.destroy_process_group()
+        return
+
+    if args.backward:
+        run_backward(args, sfb, rank, world, device, barrier)
         if use_dist:
             dist.destroy_process_group()
         return

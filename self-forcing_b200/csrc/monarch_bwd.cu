@@ -7,7 +7,8 @@
 //                P = softmax_n s,  out[a,i,j] = sum_n P_n Y_n
 // Backward, three launches per slice of (batch, head) pairs, all arithmetic in fp32:
 //   1. bwd_row_forward_kernel   recomputes aL, Y, cL into the scratch area (fp32)
-//   2. bwd_col_kernel           per slab: the softmax statistics, delta_i = sum_n P dP, then
+//   2. bwd_col_kernel           per slab, two sweeps over its keys: the softmax statistics and
+//                               delta_i = sum_n P dP (accumulated with the running maximum), then
 //                               ds = P (dP - delta), dq^_i = sum_n ds aL_n (stored to dQ),
 //                               daL_n = sum_i ds q^_i and dY_n = sum_i P dOut_i (written over aL and Y in
 //                               place, tile by tile), dcL_n = -sum_i ds
@@ -32,8 +33,8 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 constexpr int kD = kHeadDim;
-constexpr int kKs = kD + 2;        // bf16 row stride of a K / V tile in shared memory (65 words: conflict-free by row)
-constexpr int kFs = kD + 1;        // fp32 row stride of the column kernel's tiles
+constexpr int kKs = kD + 4;        // bf16 row stride of a K / V tile in shared memory (66 words: conflict-free 8-byte loads by row)
+constexpr int kFs = kD + 4;        // fp32 row stride of the column kernel's tiles: 16-byte rows, conflict-free float4 by row
 constexpr int kTileN = 32;         // keys per tile of the column kernel
 constexpr int kRowBatch = 32;      // unit rows per batch of the row kernel
 
@@ -73,8 +74,8 @@ __device__ __forceinline__ void load_kv_tile(uint32_t* dst, const bf16* src_row0
     for (int idx = tid; idx < b2 * 16; idx += nthr) {
         const int l = idx >> 4, c = idx & 15;
         const uint4 u = *reinterpret_cast<const uint4*>(src_row0 + (int64_t)l * tok_stride + c * 8);
-        uint32_t* d = dst + l * (kKs / 2) + c * 4;
-        d[0] = u.x; d[1] = u.y; d[2] = u.z; d[3] = u.w;
+        uint2* d = reinterpret_cast<uint2*>(dst + l * (kKs / 2) + c * 4);
+        d[0] = make_uint2(u.x, u.y); d[1] = make_uint2(u.z, u.w);
     }
 }
 
@@ -120,11 +121,13 @@ __global__ void __launch_bounds__(256) bwd_row_forward_kernel(const BwdParams p)
             if (l < b2) {
                 const uint32_t* kr = Ks + l * (kKs / 2);
                 float acc = 0.f;
-#pragma unroll 8
-                for (int w = 0; w < kD / 2; ++w) {
-                    const float2 kk = bf2(kr[w]);
-                    acc = fmaf(qs[2 * w], kk.x, acc);
-                    acc = fmaf(qs[2 * w + 1], kk.y, acc);
+#pragma unroll 4
+                for (int w = 0; w < kD / 4; ++w) {
+                    const uint2 kw = *reinterpret_cast<const uint2*>(kr + 2 * w);
+                    const float2 k0 = bf2(kw.x), k1 = bf2(kw.y);
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + 4 * w);
+                    acc = fmaf(qv.x, k0.x, acc); acc = fmaf(qv.y, k0.y, acc);
+                    acc = fmaf(qv.z, k1.x, acc); acc = fmaf(qv.w, k1.y, acc);
                 }
                 z[u] = acc * p.rs;
             }
@@ -201,10 +204,8 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             q4 = ld4(p.q + (int64_t)b * p.q_bs + t * tok + hd * kD + c * 4);
             d4 = ld4(p.dout + ((int64_t)b * p.n_q + t) * tok + hd * kD + c * 4);
         }
-        float* qd = qs + i * kFs + c * 4;
-        qd[0] = q4.x * p.rs; qd[1] = q4.y * p.rs; qd[2] = q4.z * p.rs; qd[3] = q4.w * p.rs;
-        float* dd = dos + i * kFs + c * 4;
-        dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+        *reinterpret_cast<float4*>(qs + i * kFs + c * 4) = make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
+        *reinterpret_cast<float4*>(dos + i * kFs + c * 4) = d4;
     }
 
     float m[T], ls[T], delta[T], dq[T][4];
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
         for (int u = 0; u < 4; ++u) dq[t][u] = 0.f;
     }
 
-    for (int pass = 0; pass < 3; ++pass) {
+    for (int pass = 0; pass < 2; ++pass) {
         for (int t0 = 0; t0 < p.n_keys; t0 += kTileN) {
             __syncthreads();                           // previous tile's readers are done (also covers qs / dos)
             for (int idx = tid; idx < kTileN * 32; idx += 256) {
@@ -223,12 +224,10 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
                 float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), y4 = a4;
                 if (t0 + n < p.n_keys) {
                     a4 = *reinterpret_cast<const float4*>(g_aL + (int64_t)(t0 + n) * kD + c * 4);
-                    if (pass > 0) y4 = *reinterpret_cast<const float4*>(g_Y + (int64_t)(t0 + n) * kD + c * 4);
+                    y4 = *reinterpret_cast<const float4*>(g_Y + (int64_t)(t0 + n) * kD + c * 4);
                 }
-                float* ad = aLs + n * kFs + c * 4;
-                ad[0] = a4.x; ad[1] = a4.y; ad[2] = a4.z; ad[3] = a4.w;
-                float* yd = Ys + n * kFs + c * 4;
-                yd[0] = y4.x; yd[1] = y4.y; yd[2] = y4.z; yd[3] = y4.w;
+                *reinterpret_cast<float4*>(aLs + n * kFs + c * 4) = a4;
+                *reinterpret_cast<float4*>(Ys + n * kFs + c * 4) = y4;
             }
             if (tid < kTileN) cls[tid] = (t0 + tid < p.n_keys) ? g_cL[t0 + tid] : 0.f;
             __syncthreads();
@@ -241,13 +240,18 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             {
                 const float* ar = aLs + lane * kFs;
                 const float* yr = Ys + lane * kFs;
-                for (int d = 0; d < kD; ++d) {
-                    const float av = ar[d];
-                    const float yv = pass > 0 ? yr[d] : 0.f;
+#pragma unroll 2
+                for (int d = 0; d < kD; d += 4) {
+                    const float4 av = *reinterpret_cast<const float4*>(ar + d);
+                    const float4 yv = *reinterpret_cast<const float4*>(yr + d);
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
-                        s[t] = fmaf(qs[(warp + 8 * t) * kFs + d], av, s[t]);
-                        if (pass > 0) dp[t] = fmaf(dos[(warp + 8 * t) * kFs + d], yv, dp[t]);
+                        const float4 qv = *reinterpret_cast<const float4*>(qs + (warp + 8 * t) * kFs + d);
+                        const float4 ov = *reinterpret_cast<const float4*>(dos + (warp + 8 * t) * kFs + d);
+                        s[t] = fmaf(qv.x, av.x, s[t]); s[t] = fmaf(qv.y, av.y, s[t]);
+                        s[t] = fmaf(qv.z, av.z, s[t]); s[t] = fmaf(qv.w, av.w, s[t]);
+                        dp[t] = fmaf(ov.x, yv.x, dp[t]); dp[t] = fmaf(ov.y, yv.y, dp[t]);
+                        dp[t] = fmaf(ov.z, yv.z, dp[t]); dp[t] = fmaf(ov.w, yv.w, dp[t]);
                     }
                 }
             }
@@ -256,27 +260,22 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             for (int t = 0; t < T; ++t) s[t] = valid ? s[t] - cl : -INFINITY;
 
             if (pass == 0) {
+                // running maximum, sum of exponentials and sum of exponentials x dP (rescaled together)
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
                     const float mn = fmaxf(m[t], wmax(s[t]));
                     const float e = valid ? __expf(s[t] - mn) : 0.f;
-                    ls[t] = ls[t] * __expf(m[t] - mn) + wsum(e);
+                    const float c = __expf(m[t] - mn);
+                    ls[t] = ls[t] * c + wsum(e);
+                    delta[t] = delta[t] * c + wsum(e * dp[t]);
                     m[t] = mn;
                 }
                 continue;
             }
-            if (pass == 1) {
-#pragma unroll
-                for (int t = 0; t < T; ++t) {
-                    const float pr = valid ? __expf(s[t] - m[t]) : 0.f;      // m holds the log-sum-exp now
-                    delta[t] += wsum(pr * dp[t]);
-                }
-                continue;
-            }
-            // pass 2
+            // pass 1
 #pragma unroll
             for (int t = 0; t < T; ++t) {
-                const float pr = valid ? __expf(s[t] - m[t]) : 0.f;
+                const float pr = valid ? __expf(s[t] - m[t]) : 0.f;          // m holds the log-sum-exp now
                 sP[(warp + 8 * t) * (kTileN + 1) + lane] = pr;
                 sDS[(warp + 8 * t) * (kTileN + 1) + lane] = pr * (dp[t] - delta[t]);
             }
@@ -335,7 +334,10 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
         }
         if (pass == 0) {
 #pragma unroll
-            for (int t = 0; t < T; ++t) m[t] = m[t] + __logf(ls[t]);
+            for (int t = 0; t < T; ++t) {
+                delta[t] = delta[t] / ls[t];
+                m[t] = m[t] + __logf(ls[t]);
+            }
         }
     }
     // dQ = sqrt(scale) dq^ (the row kernel adds its share afterwards)
@@ -366,8 +368,8 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
     float* qS = reinterpret_cast<float*>(Vs + kv_tile_words(b2));      // [kRowBatch][128]
     float* daS = qS + kRowBatch * kD;
     float* dyS = daS + kRowBatch * kD;
-    float* Rs = dyS + kRowBatch * kD;                                // [kRowBatch][b2]
-    float* dzs = Rs + kRowBatch * b2;
+    float* Rs = dyS + kRowBatch * kD;                                // [kRowBatch][4][LT]: column l at [l % 4][l / 4]
+    float* dzs = Rs + kRowBatch * 4 * LT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int d_own = tid & 127, lq = tid >> 7;
     const int64_t tok = (int64_t)p.H * kD;
@@ -413,12 +415,17 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
                         const uint32_t* kr = Ks + l * (kKs / 2);
                         const uint32_t* vr = Vs + l * (kKs / 2);
                         float az = 0.f, aa = 0.f, ay = 0.f;
-#pragma unroll 4
-                        for (int w = 0; w < kD / 2; ++w) {
-                            const float2 kk = bf2(kr[w]), vv = bf2(vr[w]);
-                            az = fmaf(qs[2 * w], kk.x, az); az = fmaf(qs[2 * w + 1], kk.y, az);
-                            aa = fmaf(as[2 * w], kk.x, aa); aa = fmaf(as[2 * w + 1], kk.y, aa);
-                            ay = fmaf(ys[2 * w], vv.x, ay); ay = fmaf(ys[2 * w + 1], vv.y, ay);
+#pragma unroll 2
+                        for (int w = 0; w < kD / 4; ++w) {
+                            const uint2 kw = *reinterpret_cast<const uint2*>(kr + 2 * w);
+                            const uint2 vw = *reinterpret_cast<const uint2*>(vr + 2 * w);
+                            const float2 k0 = bf2(kw.x), k1 = bf2(kw.y), v0 = bf2(vw.x), v1 = bf2(vw.y);
+                            const float4 qv = *reinterpret_cast<const float4*>(qs + 4 * w);
+                            const float4 av = *reinterpret_cast<const float4*>(as + 4 * w);
+                            const float4 yv = *reinterpret_cast<const float4*>(ys + 4 * w);
+                            az = fmaf(qv.x, k0.x, az); az = fmaf(qv.y, k0.y, az); az = fmaf(qv.z, k1.x, az); az = fmaf(qv.w, k1.y, az);
+                            aa = fmaf(av.x, k0.x, aa); aa = fmaf(av.y, k0.y, aa); aa = fmaf(av.z, k1.x, aa); aa = fmaf(av.w, k1.y, aa);
+                            ay = fmaf(yv.x, v0.x, ay); ay = fmaf(yv.y, v0.y, ay); ay = fmaf(yv.z, v1.x, ay); ay = fmaf(yv.w, v1.y, ay);
                         }
                         z[u] = az * p.rs;
                         ga[u] = aa * p.rs + ay;
@@ -442,12 +449,16 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int l = lane + 32 * u;
-                    if (l < b2) { Rs[slot * b2 + l] = r[u]; dzs[slot * b2 + l] = r[u] * (dr[u] - rdr); }
+                    if (l < b2) {
+                        const int at = slot * 4 * LT + (l & 3) * LT + (l >> 2);
+                        Rs[at] = r[u];
+                        dzs[at] = r[u] * (dr[u] - rdr);
+                    }
                 }
                 __syncwarp();
                 float dq[4] = {0.f, 0.f, 0.f, 0.f};
                 for (int l = 0; l < b2; ++l) {
-                    const float dz = dzs[slot * b2 + l];
+                    const float dz = dzs[slot * 4 * LT + (l & 3) * LT + (l >> 2)];
                     const float2 k0 = bf2(Ks[l * (kKs / 2) + lane]), k1 = bf2(Ks[l * (kKs / 2) + 32 + lane]);
                     dq[0] = fmaf(dz, k0.x, dq[0]); dq[1] = fmaf(dz, k0.y, dq[1]);
                     dq[2] = fmaf(dz, k1.x, dq[2]); dq[3] = fmaf(dz, k1.y, dq[3]);
@@ -464,14 +475,19 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
             const int nb = min(kRowBatch, n_rows - r0);
             for (int rr = 0; rr < nb; ++rr) {
                 const float qd = qS[rr * kD + d_own], ad = daS[rr * kD + d_own], yd = dyS[rr * kD + d_own];
+                // columns beyond b2 hold whatever shared memory held: they only reach accumulators that are never stored
 #pragma unroll
-                for (int t = 0; t < LT; ++t) {
-                    const int l = lq + 4 * t;
-                    if (l < b2) {
-                        const float rv = Rs[rr * b2 + l], dz = dzs[rr * b2 + l];
-                        accK[t] = fmaf(rv, ad, fmaf(dz, qd, accK[t]));
-                        accV[t] = fmaf(rv, yd, accV[t]);
-                    }
+                for (int t = 0; t < LT; t += 4) {
+                    const float4 rv = *reinterpret_cast<const float4*>(Rs + rr * 4 * LT + lq * LT + t);
+                    const float4 dz = *reinterpret_cast<const float4*>(dzs + rr * 4 * LT + lq * LT + t);
+                    accK[t] = fmaf(rv.x, ad, fmaf(dz.x, qd, accK[t]));
+                    accK[t + 1] = fmaf(rv.y, ad, fmaf(dz.y, qd, accK[t + 1]));
+                    accK[t + 2] = fmaf(rv.z, ad, fmaf(dz.z, qd, accK[t + 2]));
+                    accK[t + 3] = fmaf(rv.w, ad, fmaf(dz.w, qd, accK[t + 3]));
+                    accV[t] = fmaf(rv.x, yd, accV[t]);
+                    accV[t + 1] = fmaf(rv.y, yd, accV[t + 1]);
+                    accV[t + 2] = fmaf(rv.z, yd, accV[t + 2]);
+                    accV[t + 3] = fmaf(rv.w, yd, accV[t + 3]);
                 }
             }
             __syncthreads();
@@ -581,7 +597,7 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     const size_t smem_fwd = (size_t)2 * kv_tile_words(blk.b2) * 4 + 2 * 8 * kD * sizeof(float);
     const size_t smem_col = ((size_t)2 * 8 * T * kFs + 2 * kTileN * kFs + 2 * 8 * T * (kTileN + 1) + kTileN) * sizeof(float);
     const size_t smem_row = (size_t)2 * kv_tile_words(blk.b2) * 4 +
-                            ((size_t)3 * kRowBatch * kD + 2 * kRowBatch * blk.b2) * sizeof(float);
+                            ((size_t)3 * kRowBatch * kD + 2 * kRowBatch * 4 * LT) * sizeof(float);
     int bad = opt_in_smem(bwd_row_forward_kernel, smem_fwd);
     bad |= T == 4 ? opt_in_smem(bwd_col_kernel<4>, smem_col)
                   : (T == 8 ? opt_in_smem(bwd_col_kernel<8>, smem_col) : opt_in_smem(bwd_col_kernel<16>, smem_col));
