@@ -263,13 +263,16 @@ int sfm_monarch_fwd_scatter(const void* q, int64_t q_batch_stride,
  *            b1 * b2 tokens); the whole cache for 0 .. n_kv / (b1 * b2); may be null when the range
  *            is empty.  The range is how grad_only_new_kv is expressed: the groups that the call
  *            wrote.
+ *   causal_groups  0, or the block-causal mask of sfm_monarch_nocache_fwd (query group a sees the
+ *            cached groups below (a / causal_groups + 1) * causal_groups; needs n_q == n_kv):
+ *            the backward of the no-cache call, with k_cache / v_cache = its k_mon / v_mon
  *   workspace  sfm_monarch_bwd_workspace_bytes(...) bytes; the call is cut into slices of
  *            (batch, head) pairs whose scratch stays under budget_bytes (0 = 2 GiB)
  * The three kernels recompute the row step in fp32, so nothing has to be saved by the forward
  * call; dq is accumulated without atomics (results are run-to-run identical).  Block rows and
  * block columns up to 128.
  * Replaces: _attention_with_cache.backward (wan/modules/monarch_attn.py:1325-1470) and its
- * kernels (:403-596, 1034-1222).
+ * kernels (:403-596, 1034-1222), and _attention_no_cache.backward (:1565-1694).
  */
 size_t sfm_monarch_bwd_workspace_bytes(int B, int H, int D, int n_q, int n_kv,
                                        int f_tied, int h_reduce, int w_reduce, int h, int w,
@@ -281,7 +284,7 @@ int sfm_monarch_bwd(const void* q, int64_t q_batch_stride,
                     int B, int H, int D, int n_q, int n_kv,
                     int f_tied, int h_reduce, int w_reduce, int h, int w,
                     float sm_scale, int kv_group_begin, int kv_group_end,
-                    size_t budget_bytes, void* stream);
+                    int causal_groups, size_t budget_bytes, void* stream);
 
 /*
  * Launch accounting and optional per-kernel timing.  Kernel classes: 0 layout / RoPE /

@@ -39,7 +39,7 @@ SIGNATURES = {
                                 [C.c_float, C.c_size_t, C.c_void_p]),
     "sfm_monarch_bwd_workspace_bytes": (C.c_size_t, [C.c_int] * 10 + [C.c_size_t]),
     "sfm_monarch_bwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_void_p] * 5 +
-                        [C.c_size_t] + [C.c_int] * 10 + [C.c_float, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
+                        [C.c_size_t] + [C.c_int] * 10 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "sfm_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sfm_launch_count": (C.c_longlong, []),
     "sfm_profile_enable": (C.c_int, [C.c_int]),

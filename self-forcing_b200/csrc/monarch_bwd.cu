@@ -50,6 +50,11 @@ struct BwdParams {
     int H, A, F, b1, b2, n_keys, n_q;
     int bh0;                       // first (batch, head) pair of this slice
     int g0, g1;                    // cached groups whose dK / dV are wanted
+    int causal_groups;             // block-causal: query group a sees cached groups < (a / cg + 1) * cg; 0 = all
+
+    __device__ __forceinline__ int groups_seen(int a) const {
+        return causal_groups > 0 ? min(F, (a / causal_groups + 1) * causal_groups) : F;
+    }
     float scale, rs;               // softmax scale and its square root
     Blocking blk;
 };
@@ -195,6 +200,7 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
     float* g_Y = p.Y + slab * p.n_keys * kD;
     const float* g_cL = p.cL + slab * p.n_keys;
     float* g_dcL = p.dcL + slab * p.n_keys;
+    const int n_seen = p.groups_seen(a) * b1;          // keys beyond are masked: the row kernel treats their gradients as zero
 
     for (int idx = tid; idx < kRows * 32; idx += 256) {
         const int i = idx >> 5, c = idx & 31;
@@ -217,23 +223,23 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
     }
 
     for (int pass = 0; pass < 2; ++pass) {
-        for (int t0 = 0; t0 < p.n_keys; t0 += kTileN) {
+        for (int t0 = 0; t0 < n_seen; t0 += kTileN) {
             __syncthreads();                           // previous tile's readers are done (also covers qs / dos)
             for (int idx = tid; idx < kTileN * 32; idx += 256) {
                 const int n = idx >> 5, c = idx & 31;
                 float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), y4 = a4;
-                if (t0 + n < p.n_keys) {
+                if (t0 + n < n_seen) {
                     a4 = *reinterpret_cast<const float4*>(g_aL + (int64_t)(t0 + n) * kD + c * 4);
                     y4 = *reinterpret_cast<const float4*>(g_Y + (int64_t)(t0 + n) * kD + c * 4);
                 }
                 *reinterpret_cast<float4*>(aLs + n * kFs + c * 4) = a4;
                 *reinterpret_cast<float4*>(Ys + n * kFs + c * 4) = y4;
             }
-            if (tid < kTileN) cls[tid] = (t0 + tid < p.n_keys) ? g_cL[t0 + tid] : 0.f;
+            if (tid < kTileN) cls[tid] = (t0 + tid < n_seen) ? g_cL[t0 + tid] : 0.f;
             __syncthreads();
 
             // logits (and dP = dOut_i . Y_n) for key `lane`, rows warp + 8 t
-            const bool valid = t0 + lane < p.n_keys;
+            const bool valid = t0 + lane < n_seen;
             float s[T], dp[T];
 #pragma unroll
             for (int t = 0; t < T; ++t) { s[t] = 0.f; dp[t] = 0.f; }
@@ -317,7 +323,7 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const int n = t0 + warp + 8 * v;
-                    if (n < p.n_keys) {
+                    if (n < n_seen) {
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             g_aL[(int64_t)n * kD + lane + 32 * u] = ga[v][u];
@@ -326,7 +332,7 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
                     }
                 }
             }
-            if (tid < kTileN && t0 + tid < p.n_keys) {
+            if (tid < kTileN && t0 + tid < n_seen) {
                 float acc = 0.f;
                 for (int i = 0; i < b1; ++i) acc += sDS[i * (kTileN + 1) + tid];
                 g_dcL[t0 + tid] = -acc;
@@ -396,9 +402,12 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
                 const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
                 const int64_t o = (slab * p.n_keys + n) * kD;
                 const float4 q4 = ld4(p.q + (int64_t)b * p.q_bs + t_nat * tok + hd * kD + lane * 4);
-                const float4 a4 = *reinterpret_cast<const float4*>(p.aL + o + lane * 4);
-                const float4 y4 = *reinterpret_cast<const float4*>(p.Y + o + lane * 4);
-                const float dcl = p.dcL[slab * p.n_keys + n];
+                // a pair (a, f) the query group may not see has zero gradients (its scratch rows still hold forward values)
+                const bool seen = f < p.groups_seen(a);
+                const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 a4 = seen ? *reinterpret_cast<const float4*>(p.aL + o + lane * 4) : zero4;
+                const float4 y4 = seen ? *reinterpret_cast<const float4*>(p.Y + o + lane * 4) : zero4;
+                const float dcl = seen ? p.dcL[slab * p.n_keys + n] : 0.f;
                 float* qs = qS + slot * kD;
                 float* as = daS + slot * kD;
                 float* ys = dyS + slot * kD;
@@ -566,12 +575,13 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
                                int64_t kv_batch_stride, const void* dout, void* dq, void* dk, void* dv, void* workspace,
                                size_t workspace_bytes, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce,
                                int w_reduce, int h, int w, float sm_scale, int kv_group_begin, int kv_group_end,
-                               size_t budget_bytes, void* stream) {
+                               int causal_groups, size_t budget_bytes, void* stream) {
     if (!q || !k_cache || !v_cache || !dout || !dq || !workspace) return SFM_ERR_NULL_POINTER;
     BwdPlan pl;
     if (int rc = make_bwd_plan(&pl, B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, budget_bytes)) return rc;
     if (!(sm_scale > 0.f)) return SFM_ERR_BAD_SHAPE;
     if (kv_group_begin < 0 || kv_group_end > pl.F || kv_group_begin > kv_group_end) return SFM_ERR_BAD_SHAPE;
+    if (causal_groups < 0 || (causal_groups > 0 && (pl.A != pl.F || pl.A % causal_groups))) return SFM_ERR_BAD_SHAPE;
     if (kv_group_end > kv_group_begin && (!dk || !dv)) return SFM_ERR_NULL_POINTER;
     if (workspace_bytes < pl.total) return SFM_ERR_WORKSPACE;
     for (const void* ptr : {q, k_cache, v_cache, dout, (const void*)dq, (const void*)dk, (const void*)dv,
@@ -589,6 +599,7 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     p.q_bs = q_batch_stride; p.kv_bs = kv_batch_stride;
     p.H = H; p.A = pl.A; p.F = pl.F; p.b1 = blk.b1; p.b2 = blk.b2; p.n_keys = pl.n_keys; p.n_q = n_q;
     p.g0 = kv_group_begin; p.g1 = kv_group_end;
+    p.causal_groups = causal_groups;
     p.scale = sm_scale; p.rs = sqrtf(sm_scale);
     p.blk = blk;
 

@@ -167,7 +167,8 @@ def _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale
 
 
 def monarch_attn_with_kv_cache_backward(q, k_cache, v_cache, grad_out, f_tied, h_reduce, w_reduce, h, w, sm_scale=None,
-                                        kv_groups: Optional[Tuple[int, int]] = None, budget_bytes: int = 0):
+                                        kv_groups: Optional[Tuple[int, int]] = None, budget_bytes: int = 0,
+                                        causal_groups: int = 0):
     """Gradients of ``monarch_attn_with_kv_cache`` (single pass) for a gradient ``grad_out`` of its output.
 
     q, grad_out: [B, n_q, H, 128] bf16, natural token order; k_cache / v_cache: the cache view the forward
@@ -175,7 +176,8 @@ def monarch_attn_with_kv_cache_backward(q, k_cache, v_cache, grad_out, f_tied, h
     those cached groups (one group = b1 * b2 tokens, a frame for the framewise blocking); None = all.
     Returns (dq fp32 [B, n_q, H, 128] natural order, dk, dv bf16 [B, groups * b1 * b2, H, 128] Monarch
     order).  The call runs in slices of (batch, head) pairs whose fp32 scratch stays under ``budget_bytes``
-    (0 = 2 GiB).  Stands in for _attention_with_cache.backward (monarch_attn.py:1325-1470)."""
+    (0 = 2 GiB).  ``causal_groups`` > 0 applies the block-causal mask of ``monarch_attn`` (query group a sees
+    the groups below (a // causal_groups + 1) * causal_groups).  Stands in for _attention_with_cache.backward (monarch_attn.py:1325-1470)."""
     for t, name in ((q, "q"), (grad_out, "grad_out")):
         _require(t, name)
     _cache_view_ok(k_cache, "k_cache")
@@ -201,7 +203,8 @@ def monarch_attn_with_kv_cache_backward(q, k_cache, v_cache, grad_out, f_tied, h
     rc = lib.sfm_monarch_bwd(_ptr(q), _batch_stride(q), _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache),
                              _ptr(grad_out), _ptr(dq), _ptr(dk) if dk.numel() else None,
                              _ptr(dv) if dv.numel() else None, _ptr(ws), ws.numel(), B, H, D, n_q, n_kv, f_tied,
-                             h_reduce, w_reduce, h, w, float(sm_scale), g0, g1, budget_bytes, _stream())
+                             h_reduce, w_reduce, h, w, float(sm_scale), g0, g1, int(causal_groups), budget_bytes,
+                             _stream())
     _lib.check(rc, "sfm_monarch_bwd")
     return dq, dk, dv
 
@@ -242,6 +245,28 @@ class _MonarchWithKVCacheFn(torch.autograd.Function):
             d_kc[:, start:end] = 0
             d_vc[:, start:end] = 0
         return dq, d_new_k, d_new_v, d_kc, d_vc, None, None, None, None, None
+
+
+class _MonarchNoCacheFn(torch.autograd.Function):
+    """monarch_attn (no cache, optionally block-causal) with the backward kernels behind it."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, blocking, sm_scale, block_causal_size):
+        out, k_mon, v_mon, causal_groups = _monarch_attn_fwd(q.detach(), k.detach(), v.detach(), *blocking, sm_scale,
+                                                             block_causal_size, 1)
+        ctx.save_for_backward(q, k_mon, v_mon)
+        ctx.args = (blocking, sm_scale, causal_groups)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k_mon, v_mon = ctx.saved_tensors
+        blocking, sm_scale, causal_groups = ctx.args
+        dq, dk, dv = monarch_attn_with_kv_cache_backward(q, k_mon, v_mon, grad_out.to(q.dtype), *blocking, sm_scale,
+                                                         causal_groups=causal_groups)
+        nat2mon, _ = build_maps(k_mon.shape[1], *blocking)
+        idx = torch.from_numpy(nat2mon.astype(np.int64)).to(q.device)
+        return dq, dk.index_select(1, idx), dv.index_select(1, idx), None, None, None
 
 
 # ------------------------------------------------------------------------------------- public
@@ -395,7 +420,18 @@ def rope_monarch_attn_with_kv_cache_sharded(q_shards, k_shards, v_shards, out_sh
 
 def monarch_attn(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale=None, block_causal_size=None, num_iters=1):
     """Same contract as the reference's monarch_attn (monarch_attn.py:1753-1776): no cache;
-    with block_causal_size, causal over blocks of that many tokens (forward only)."""
+    with block_causal_size, causal over blocks of that many tokens.  Under autograd (an input requires a
+    gradient) the single-pass variant goes through an autograd function backed by the backward kernels."""
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v)):
+        if num_iters != 1:
+            raise NotImplementedError("the backward pass exists for num_iters == 1 only")
+        return _MonarchNoCacheFn.apply(q, k, v, (f_tied, h_reduce, w_reduce, h, w), sm_scale, block_causal_size)
+    return _monarch_attn_fwd(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale, block_causal_size, num_iters)[0]
+
+
+def _monarch_attn_fwd(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale, block_causal_size, num_iters):
+    """Forward of monarch_attn; returns (out, k_mon, v_mon, causal_groups): the keys / values in Monarch block
+    order are what the backward kernels read."""
     for t, name in ((q, "q"), (k, "k"), (v, "v")):
         _require(t, name)
     B, N, H, D = q.shape
@@ -422,7 +458,7 @@ def monarch_attn(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale=None, block
                                       n_kv * H * D, _ptr(None), B, n_kv, H, D, 0, f_tied, h_reduce, w_reduce, h, w,
                                       0, 1, _stream())
         _lib.check(rc, "sfm_rope_cache_write")
-        return _monarch_fwd(q, k_mon, v_mon, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
+        return _monarch_fwd(q, k_mon, v_mon, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters), k_mon, v_mon, 0
     nbytes = lib.sfm_monarch_workspace_bytes(B, H, D, N, N, f_tied, h_reduce, w_reduce, h, w, num_iters, 0) or 256
     ws = _workspace(q.device, nbytes)
     out = torch.empty_like(q)
@@ -432,7 +468,7 @@ def monarch_attn(q, k, v, f_tied, h_reduce, w_reduce, h, w, sm_scale=None, block
                                      ws.numel(), B, H, D, N, f_tied, h_reduce, w_reduce, h, w, float(sm_scale),
                                      causal_groups, int(num_iters), 0, _stream())
     _lib.check(rc, "sfm_monarch_nocache_fwd")
-    return out
+    return out, k_mon, v_mon, causal_groups
 
 
 def flash_attention(q, k, v, q_lens=None, k_lens=None, dropout_p=0., softmax_scale=None, q_scale=None,

@@ -111,13 +111,16 @@ def test_entry_points_validate_arguments_without_a_gpu(sfb):
     # backward: null gradient, workspace too small, group range outside the cache, block rows above 128
     big = 1 << 40
     assert lib.sfm_monarch_bwd(one, 0, one, one, 0, null, one, one, one, one, big, 1, 1, 128, 1560, 3120, 1, 1, 1,
-                               30, 52, 1.0, 0, 2, 0, null) == -1
+                               30, 52, 1.0, 0, 2, 0, 0, null) == -1
     assert lib.sfm_monarch_bwd(one, 0, one, one, 0, one, one, one, one, one, 0, 1, 1, 128, 1560, 3120, 1, 1, 1,
-                               30, 52, 1.0, 0, 2, 0, null) == -5
+                               30, 52, 1.0, 0, 2, 0, 0, null) == -5
     assert lib.sfm_monarch_bwd(one, 0, one, one, 0, one, one, one, one, one, big, 1, 1, 128, 1560, 3120, 1, 1, 1,
-                               30, 52, 1.0, 1, 3, 0, null) == -2
+                               30, 52, 1.0, 1, 3, 0, 0, null) == -2
     assert lib.sfm_monarch_bwd(one, 0, one, one, 0, one, one, null, null, one, big, 1, 1, 128, 1560, 3120, 1, 1, 1,
-                               30, 52, 1.0, 0, 2, 0, null) == -1
+                               30, 52, 1.0, 0, 2, 0, 0, null) == -1
+    # block-causal needs n_q == n_kv
+    assert lib.sfm_monarch_bwd(one, 0, one, one, 0, one, one, one, one, one, big, 1, 1, 128, 1560, 3120, 1, 1, 1,
+                               30, 52, 1.0, 0, 2, 1, 0, null) == -2
     assert lib.sfm_monarch_bwd_workspace_bytes(1, 1, 128, 5 * 30 * 52, 5 * 30 * 52, 5, 1, 1, 30, 52, 0) == 0
     per_bh = 1 * 52 * (2 * 30) * (2 * 128 + 2) * 4
     assert 2 * per_bh <= lib.sfm_monarch_bwd_workspace_bytes(1, 2, 128, 1560, 3120, 1, 1, 1, 30, 52, 0) <= 2 * per_bh + 1024

@@ -160,3 +160,29 @@ def test_autograd_function(sfb, only_new):
         grad_close(kv.grad, ref["kc"], 1e-2, "k_cache.grad")
         grad_close(vv.grad, ref["vc"], 1e-2, "v_cache.grad")
         assert not kv.grad[:, c["start"]:c["end"]].any()
+
+
+@pytest.mark.parametrize("ci,causal_frames", [(0, None), (0, 2), (2, 1), (1, None), (3, 3)])
+def test_nocache_autograd(sfb, ci, causal_frames):
+    """monarch_attn under autograd, plain and block-causal: gradients of q, k, v in natural token order against
+    autograd through the oracle."""
+    _, ft, hr, wr, h, w = cases.SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(8600 + 10 * ci + (causal_frames or 0))
+    n = 6 * ft * h * w
+    B, H = 1, 2
+    mk = lambda: bf(cases.randn(rng, B, n, H, 128))
+    q, k, v, g = mk(), mk(), mk(), mk()
+    bcs = None if causal_frames is None else causal_frames * ft * h * w
+    q32, k32, v32 = (t.float().requires_grad_() for t in (q, k, v))
+    z_ref = orc.monarch_attn(q32, k32, v32, ft, hr, wr, h, w, block_causal_size=bcs)
+    (z_ref * g.float()).sum().backward()
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    z = sfb.monarch_attn(qg, kg, vg, ft, hr, wr, h, w, block_causal_size=bcs)
+    with torch.no_grad():
+        z_plain = sfb.monarch_attn(q.cuda(), k.cuda(), v.cuda(), ft, hr, wr, h, w, block_causal_size=bcs)
+    assert torch.equal(z, z_plain)
+    (z.float() * g.cuda().float()).sum().backward()
+    torch.cuda.synchronize()
+    grad_close(qg.grad, q32.grad, 1e-2, "q.grad")
+    grad_close(kg.grad, k32.grad, 1e-2, "k.grad")
+    grad_close(vg.grad, v32.grad, 1e-2, "v.grad")

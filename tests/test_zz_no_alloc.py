@@ -8,6 +8,7 @@ call's contents), and also checks that an oversized problem is refused without a
 file name sorts last so that a run stopping at the first failure has already run everything else.
 """
 import ctypes as C
+import gc
 
 import numpy as np
 import pytest
@@ -35,6 +36,7 @@ def _run_both(lib, q, kc, vc, blocking, n_kv, num_iters=1):
     assert rc == 0, lib.sfm_error_string(rc)
 
     got = torch.full_like(q, float("nan"))
+    gc.collect()                                            # garbage of earlier tests must not be freed in between
     before = torch.cuda.memory_allocated()
     rc = lib.sfm_monarch_fwd_static(_ptr(q), q_bs, _ptr(kc), _ptr(vc), cache_bs, _ptr(got), B, H, D, n_q, n_kv,
                                     ft, hr, wr, h, w, D ** -0.5, num_iters, stream)
