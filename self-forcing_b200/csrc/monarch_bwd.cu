@@ -72,6 +72,11 @@ __device__ __forceinline__ float wmax(float v) {
 __device__ __forceinline__ float2 bf2(uint32_t w) {
     return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
 }
+__device__ __forceinline__ float f2_hsum(uint64_t v) {
+    float lo, hi;
+    f2_unpack(v, lo, hi);
+    return lo + hi;
+}
 
 // K or V rows [b2][128] bf16 of cached group f, block row k -> shared memory (row stride kKs).
 __device__ __forceinline__ void load_kv_tile(uint32_t* dst, const bf16* src_row0, int64_t tok_stride, int b2, int tid,
@@ -387,116 +392,146 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
         __syncthreads();                                             // the previous group's readers are done
         load_kv_tile(Ks, p.k + kv_off, tok, b2, tid, 512);
         load_kv_tile(Vs, p.v + kv_off, tok, b2, tid, 512);
-        float accK[LT], accV[LT];
+        uint64_t accK[LT / 2], accV[LT / 2];                         // packed pairs: columns lq + 4 (2 i), lq + 4 (2 i + 1)
 #pragma unroll
-        for (int t = 0; t < LT; ++t) { accK[t] = 0.f; accV[t] = 0.f; }
+        for (int t = 0; t < LT / 2; ++t) { accK[t] = 0; accV[t] = 0; }
         __syncthreads();
 
         for (int r0 = 0; r0 < n_rows; r0 += kRowBatch) {
-            // ---- phase 1: rows r0 + warp and r0 + warp + 16
-            for (int slot = warp; slot < kRowBatch; slot += 16) {
-                const int row = r0 + slot;
-                if (row >= n_rows) break;
-                const int a = row / b2, j = row - a * b2;
-                const int64_t t_nat = p.blk.row_token(a, k) + j;
-                const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
-                const int64_t o = (slab * p.n_keys + n) * kD;
-                const float4 q4 = ld4(p.q + (int64_t)b * p.q_bs + t_nat * tok + hd * kD + lane * 4);
-                // a pair (a, f) the query group may not see has zero gradients (its scratch rows still hold forward values)
-                const bool seen = f < p.groups_seen(a);
-                const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float4 a4 = seen ? *reinterpret_cast<const float4*>(p.aL + o + lane * 4) : zero4;
-                const float4 y4 = seen ? *reinterpret_cast<const float4*>(p.Y + o + lane * 4) : zero4;
-                const float dcl = seen ? p.dcL[slab * p.n_keys + n] : 0.f;
-                float* qs = qS + slot * kD;
-                float* as = daS + slot * kD;
-                float* ys = dyS + slot * kD;
-                *reinterpret_cast<float4*>(qs + lane * 4) = make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
-                *reinterpret_cast<float4*>(as + lane * 4) = a4;
-                *reinterpret_cast<float4*>(ys + lane * 4) = y4;
+            // ---- phase 1: each warp takes rows r0 + warp and r0 + warp + 16 together, so that every K / V element it
+            //      reads from shared memory serves both; a missing second row repeats the first into a slot nobody reads
+            if (r0 + warp < n_rows) {
+                const bool two = r0 + warp + 16 < n_rows;
+                int64_t t_nat[2];
+                float dcl[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int row = r0 + warp + ((e == 1 && two) ? 16 : 0);
+                    const int slot = warp + 16 * e;
+                    const int a = row / b2, j = row - a * b2;
+                    t_nat[e] = p.blk.row_token(a, k) + j;
+                    const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
+                    const int64_t o = (slab * p.n_keys + n) * kD;
+                    const float4 q4 = ld4(p.q + (int64_t)b * p.q_bs + t_nat[e] * tok + hd * kD + lane * 4);
+                    // a pair (a, f) the query group may not see has zero gradients (its scratch rows still hold forward values)
+                    const bool seen = f < p.groups_seen(a);
+                    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 a4 = seen ? *reinterpret_cast<const float4*>(p.aL + o + lane * 4) : zero4;
+                    const float4 y4 = seen ? *reinterpret_cast<const float4*>(p.Y + o + lane * 4) : zero4;
+                    dcl[e] = seen ? p.dcL[slab * p.n_keys + n] : 0.f;
+                    *reinterpret_cast<float4*>(qS + slot * kD + lane * 4) =
+                        make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
+                    *reinterpret_cast<float4*>(daS + slot * kD + lane * 4) = a4;
+                    *reinterpret_cast<float4*>(dyS + slot * kD + lane * 4) = y4;
+                }
                 __syncwarp();
-                float z[4], ga[4], mx = -INFINITY;
+                float z[2][4], ga[2][4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int l = lane + 32 * u;
-                    z[u] = -INFINITY; ga[u] = 0.f;
+                    z[0][u] = z[1][u] = -INFINITY; ga[0][u] = ga[1][u] = 0.f;
                     if (l < b2) {
                         const uint32_t* kr = Ks + l * (kKs / 2);
                         const uint32_t* vr = Vs + l * (kKs / 2);
-                        float az = 0.f, aa = 0.f, ay = 0.f;
+                        uint64_t az[2] = {0, 0}, aa[2] = {0, 0}, ay[2] = {0, 0};      // packed (even d, odd d) partial sums
 #pragma unroll 2
                         for (int w = 0; w < kD / 4; ++w) {
                             const uint2 kw = *reinterpret_cast<const uint2*>(kr + 2 * w);
                             const uint2 vw = *reinterpret_cast<const uint2*>(vr + 2 * w);
                             const float2 k0 = bf2(kw.x), k1 = bf2(kw.y), v0 = bf2(vw.x), v1 = bf2(vw.y);
-                            const float4 qv = *reinterpret_cast<const float4*>(qs + 4 * w);
-                            const float4 av = *reinterpret_cast<const float4*>(as + 4 * w);
-                            const float4 yv = *reinterpret_cast<const float4*>(ys + 4 * w);
-                            az = fmaf(qv.x, k0.x, az); az = fmaf(qv.y, k0.y, az); az = fmaf(qv.z, k1.x, az); az = fmaf(qv.w, k1.y, az);
-                            aa = fmaf(av.x, k0.x, aa); aa = fmaf(av.y, k0.y, aa); aa = fmaf(av.z, k1.x, aa); aa = fmaf(av.w, k1.y, aa);
-                            ay = fmaf(yv.x, v0.x, ay); ay = fmaf(yv.y, v0.y, ay); ay = fmaf(yv.z, v1.x, ay); ay = fmaf(yv.w, v1.y, ay);
+                            const uint64_t k01 = f2_pack(k0.x, k0.y), k23 = f2_pack(k1.x, k1.y);
+                            const uint64_t v01 = f2_pack(v0.x, v0.y), v23 = f2_pack(v1.x, v1.y);
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int slot = warp + 16 * e;
+                                const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qS + slot * kD + 4 * w);
+                                const ulonglong2 av = *reinterpret_cast<const ulonglong2*>(daS + slot * kD + 4 * w);
+                                const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(dyS + slot * kD + 4 * w);
+                                az[e] = f2_fma(qv.x, k01, az[e]); az[e] = f2_fma(qv.y, k23, az[e]);
+                                aa[e] = f2_fma(av.x, k01, aa[e]); aa[e] = f2_fma(av.y, k23, aa[e]);
+                                ay[e] = f2_fma(yv.x, v01, ay[e]); ay[e] = f2_fma(yv.y, v23, ay[e]);
+                            }
                         }
-                        z[u] = az * p.rs;
-                        ga[u] = aa * p.rs + ay;
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            z[e][u] = f2_hsum(az[e]) * p.rs;
+                            ga[e][u] = f2_hsum(aa[e]) * p.rs + f2_hsum(ay[e]);
+                        }
                     }
-                    mx = fmaxf(mx, z[u]);
                 }
-                mx = wmax(mx);
-                float e[4], sum = 0.f;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) { e[u] = (lane + 32 * u < b2) ? __expf(z[u] - mx) : 0.f; sum += e[u]; }
-                sum = wsum(sum);
-                const float lse = mx + __logf(sum), inv = 1.f / sum;
-                float r[4], dr[4], rdr = 0.f;
+                for (int e = 0; e < 2; ++e) {
+                    const int slot = warp + 16 * e;
+                    float mx = fmaxf(fmaxf(z[e][0], z[e][1]), fmaxf(z[e][2], z[e][3]));
+                    mx = wmax(mx);
+                    float ex[4], sum = 0.f;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    r[u] = e[u] * inv;
-                    dr[u] = (lane + 32 * u < b2) ? ga[u] + dcl * (z[u] - lse + 1.f) : 0.f;
-                    rdr += r[u] * dr[u];
-                }
-                rdr = wsum(rdr);
+                    for (int u = 0; u < 4; ++u) { ex[u] = (lane + 32 * u < b2) ? __expf(z[e][u] - mx) : 0.f; sum += ex[u]; }
+                    sum = wsum(sum);
+                    const float lse = mx + __logf(sum), inv = 1.f / sum;
+                    float r[4], dr[4], rdr = 0.f;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int l = lane + 32 * u;
-                    if (l < b2) {
-                        const int at = slot * 4 * LT + (l & 3) * LT + (l >> 2);
-                        Rs[at] = r[u];
-                        dzs[at] = r[u] * (dr[u] - rdr);
+                    for (int u = 0; u < 4; ++u) {
+                        r[u] = ex[u] * inv;
+                        dr[u] = (lane + 32 * u < b2) ? ga[e][u] + dcl[e] * (z[e][u] - lse + 1.f) : 0.f;
+                        rdr += r[u] * dr[u];
+                    }
+                    rdr = wsum(rdr);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int l = lane + 32 * u;
+                        if (l < b2) {
+                            const int at = slot * 4 * LT + (l & 3) * LT + (l >> 2);
+                            Rs[at] = r[u];
+                            dzs[at] = r[u] * (dr[u] - rdr);
+                        }
                     }
                 }
                 __syncwarp();
-                float dq[4] = {0.f, 0.f, 0.f, 0.f};
+                uint64_t dq01[2] = {0, 0}, dq23[2] = {0, 0};
+#pragma unroll 2
                 for (int l = 0; l < b2; ++l) {
-                    const float dz = dzs[slot * 4 * LT + (l & 3) * LT + (l >> 2)];
                     const float2 k0 = bf2(Ks[l * (kKs / 2) + lane]), k1 = bf2(Ks[l * (kKs / 2) + 32 + lane]);
-                    dq[0] = fmaf(dz, k0.x, dq[0]); dq[1] = fmaf(dz, k0.y, dq[1]);
-                    dq[2] = fmaf(dz, k1.x, dq[2]); dq[3] = fmaf(dz, k1.y, dq[3]);
+                    const uint64_t k01 = f2_pack(k0.x, k0.y), k23 = f2_pack(k1.x, k1.y);
+                    const int at = (l & 3) * LT + (l >> 2);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float dz = dzs[(warp + 16 * e) * 4 * LT + at];
+                        const uint64_t dz2 = f2_pack(dz, dz);
+                        dq01[e] = f2_fma(dz2, k01, dq01[e]);
+                        dq23[e] = f2_fma(dz2, k23, dq23[e]);
+                    }
                 }
-                float* g = p.dq + (((int64_t)b * p.n_q + t_nat) * p.H + hd) * kD;
-                float2 g0 = *reinterpret_cast<float2*>(g + 2 * lane), g1 = *reinterpret_cast<float2*>(g + 64 + 2 * lane);
-                g0.x += p.scale * dq[0]; g0.y += p.scale * dq[1];
-                g1.x += p.scale * dq[2]; g1.y += p.scale * dq[3];
-                *reinterpret_cast<float2*>(g + 2 * lane) = g0;
-                *reinterpret_cast<float2*>(g + 64 + 2 * lane) = g1;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    if (e == 0 || two) {
+                        float d0, d1, d2, d3;
+                        f2_unpack(dq01[e], d0, d1);
+                        f2_unpack(dq23[e], d2, d3);
+                        float* g = p.dq + (((int64_t)b * p.n_q + t_nat[e]) * p.H + hd) * kD;
+                        float2 g0 = *reinterpret_cast<float2*>(g + 2 * lane), g1 = *reinterpret_cast<float2*>(g + 64 + 2 * lane);
+                        g0.x += p.scale * d0; g0.y += p.scale * d1;
+                        g1.x += p.scale * d2; g1.y += p.scale * d3;
+                        *reinterpret_cast<float2*>(g + 2 * lane) = g0;
+                        *reinterpret_cast<float2*>(g + 64 + 2 * lane) = g1;
+                    }
+                }
             }
             __syncthreads();
             // ---- phase 2
             const int nb = min(kRowBatch, n_rows - r0);
             for (int rr = 0; rr < nb; ++rr) {
                 const float qd = qS[rr * kD + d_own], ad = daS[rr * kD + d_own], yd = dyS[rr * kD + d_own];
+                const uint64_t qd2 = f2_pack(qd, qd), ad2 = f2_pack(ad, ad), yd2 = f2_pack(yd, yd);
                 // columns beyond b2 hold whatever shared memory held: they only reach accumulators that are never stored
 #pragma unroll
                 for (int t = 0; t < LT; t += 4) {
-                    const float4 rv = *reinterpret_cast<const float4*>(Rs + rr * 4 * LT + lq * LT + t);
-                    const float4 dz = *reinterpret_cast<const float4*>(dzs + rr * 4 * LT + lq * LT + t);
-                    accK[t] = fmaf(rv.x, ad, fmaf(dz.x, qd, accK[t]));
-                    accK[t + 1] = fmaf(rv.y, ad, fmaf(dz.y, qd, accK[t + 1]));
-                    accK[t + 2] = fmaf(rv.z, ad, fmaf(dz.z, qd, accK[t + 2]));
-                    accK[t + 3] = fmaf(rv.w, ad, fmaf(dz.w, qd, accK[t + 3]));
-                    accV[t] = fmaf(rv.x, yd, accV[t]);
-                    accV[t + 1] = fmaf(rv.y, yd, accV[t + 1]);
-                    accV[t + 2] = fmaf(rv.z, yd, accV[t + 2]);
-                    accV[t + 3] = fmaf(rv.w, yd, accV[t + 3]);
+                    const ulonglong2 rv = *reinterpret_cast<const ulonglong2*>(Rs + rr * 4 * LT + lq * LT + t);
+                    const ulonglong2 dz = *reinterpret_cast<const ulonglong2*>(dzs + rr * 4 * LT + lq * LT + t);
+                    accK[t / 2] = f2_fma(rv.x, ad2, f2_fma(dz.x, qd2, accK[t / 2]));
+                    accK[t / 2 + 1] = f2_fma(rv.y, ad2, f2_fma(dz.y, qd2, accK[t / 2 + 1]));
+                    accV[t / 2] = f2_fma(rv.x, yd2, accV[t / 2]);
+                    accV[t / 2 + 1] = f2_fma(rv.y, yd2, accV[t / 2 + 1]);
                 }
             }
             __syncthreads();
@@ -504,12 +539,18 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
         if (f >= p.g0 && f < p.g1) {
             const int64_t base = (int64_t)b * (p.g1 - p.g0) * p.b1 * b2 + ((int64_t)(f - p.g0) * p.b1 + k) * b2;
 #pragma unroll
-            for (int t = 0; t < LT; ++t) {
-                const int l = lq + 4 * t;
-                if (l < b2) {
-                    const int64_t o = ((base + l) * p.H + hd) * kD + d_own;
-                    p.dk[o] = __float2bfloat16(accK[t] * p.rs);
-                    p.dv[o] = __float2bfloat16(accV[t]);
+            for (int t = 0; t < LT; t += 2) {
+                float gk[2], gv[2];
+                f2_unpack(accK[t / 2], gk[0], gk[1]);
+                f2_unpack(accV[t / 2], gv[0], gv[1]);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int l = lq + 4 * (t + e);
+                    if (l < b2) {
+                        const int64_t o = ((base + l) * p.H + hd) * kD + d_own;
+                        p.dk[o] = __float2bfloat16(gk[e] * p.rs);
+                        p.dv[o] = __float2bfloat16(gv[e]);
+                    }
                 }
             }
         }
