@@ -97,7 +97,7 @@ __device__ __forceinline__ float4 ld4(const bf16* p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// 1. forward recompute of the row step.  grid (n_keys, slice of batch*head), 256 threads; a warp per unit row.
+// 1. forward recompute of the row step.  grid (n_keys, slice of batch*head), 256 threads; a warp per pair of unit rows.
 // ---------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) bwd_row_forward_kernel(const BwdParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -105,79 +105,109 @@ __global__ void __launch_bounds__(256) bwd_row_forward_kernel(const BwdParams p)
     const int bhl = blockIdx.y, bh = p.bh0 + bhl, b = bh / p.H, hd = bh - b * p.H;
     uint32_t* Ks = reinterpret_cast<uint32_t*>(smem);
     uint32_t* Vs = Ks + kv_tile_words(b2);
-    float* qrow = reinterpret_cast<float*>(Vs + kv_tile_words(b2));      // [8][128]
-    float* rrow = qrow + 8 * kD;                                       // [8][128]
+    float* qrow = reinterpret_cast<float*>(Vs + kv_tile_words(b2));      // [8 warps][2 rows][128]
+    float* rrow = qrow + 8 * 2 * kD;                                   // [8 warps][2 rows][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t tok = (int64_t)p.H * kD;
     const int64_t kv_off = (int64_t)b * p.kv_bs + ((int64_t)n * b2) * tok + hd * kD;
     load_kv_tile(Ks, p.k + kv_off, tok, b2, threadIdx.x, 256);
     load_kv_tile(Vs, p.v + kv_off, tok, b2, threadIdx.x, 256);
     __syncthreads();
-    float* qs = qrow + warp * kD;
-    float* rs_ = rrow + warp * kD;
-    for (int row = warp; row < p.A * b2; row += 8) {
-        const int a = row / b2, j = row - a * b2;
-        const bf16* qp = p.q + (int64_t)b * p.q_bs + (int64_t)(p.blk.row_token(a, k) + j) * tok + hd * kD;
-        const float4 q4 = ld4(qp + lane * 4);
+    float* qs = qrow + warp * 2 * kD;                                  // two unit rows per warp at a time
+    float* rs_ = rrow + warp * 2 * kD;
+    const int n_rows = p.A * b2;
+    for (int row0 = warp; row0 < n_rows; row0 += 16) {
+        // rows row0 and row0 + 8 share every K / V element read from shared memory; a missing second row repeats the first
+        const bool two = row0 + 8 < n_rows;
+        int64_t out_at[2], cl_at[2];
         __syncwarp();
-        qs[lane * 4 + 0] = q4.x * p.rs; qs[lane * 4 + 1] = q4.y * p.rs;
-        qs[lane * 4 + 2] = q4.z * p.rs; qs[lane * 4 + 3] = q4.w * p.rs;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int row = row0 + ((e == 1 && two) ? 8 : 0);
+            const int a = row / b2, j = row - a * b2;
+            const bf16* qp = p.q + (int64_t)b * p.q_bs + (int64_t)(p.blk.row_token(a, k) + j) * tok + hd * kD;
+            const float4 q4 = ld4(qp + lane * 4);
+            *reinterpret_cast<float4*>(qs + e * kD + lane * 4) = make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
+            const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
+            cl_at[e] = slab * p.n_keys + n;
+            out_at[e] = cl_at[e] * kD;
+        }
         __syncwarp();
-        float z[4], mx = -INFINITY;
+        float z[2][4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int l = lane + 32 * u;
-            z[u] = -INFINITY;
+            z[0][u] = z[1][u] = -INFINITY;
             if (l < b2) {
                 const uint32_t* kr = Ks + l * (kKs / 2);
-                float acc = 0.f;
+                uint64_t acc[2] = {0, 0};                                  // packed (even d, odd d) partial sums
 #pragma unroll 4
                 for (int w = 0; w < kD / 4; ++w) {
                     const uint2 kw = *reinterpret_cast<const uint2*>(kr + 2 * w);
                     const float2 k0 = bf2(kw.x), k1 = bf2(kw.y);
-                    const float4 qv = *reinterpret_cast<const float4*>(qs + 4 * w);
-                    acc = fmaf(qv.x, k0.x, acc); acc = fmaf(qv.y, k0.y, acc);
-                    acc = fmaf(qv.z, k1.x, acc); acc = fmaf(qv.w, k1.y, acc);
+                    const uint64_t k01 = f2_pack(k0.x, k0.y), k23 = f2_pack(k1.x, k1.y);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qs + e * kD + 4 * w);
+                        acc[e] = f2_fma(qv.x, k01, acc[e]);
+                        acc[e] = f2_fma(qv.y, k23, acc[e]);
+                    }
                 }
-                z[u] = acc * p.rs;
-            }
-            mx = fmaxf(mx, z[u]);
-        }
-        mx = wmax(mx);
-        float e[4], sum = 0.f;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) { e[u] = (lane + 32 * u < b2) ? __expf(z[u] - mx) : 0.f; sum += e[u]; }
-        sum = wsum(sum);
-        const float lse = mx + __logf(sum), inv = 1.f / sum;
-        float cl = 0.f;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int l = lane + 32 * u;
-            if (l < b2) {
-                const float r = e[u] * inv;
-                rs_[l] = r;
-                cl += r * (z[u] - lse);
+                z[0][u] = f2_hsum(acc[0]) * p.rs;
+                z[1][u] = f2_hsum(acc[1]) * p.rs;
             }
         }
-        cl = wsum(cl);
+        float cl[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float mx = wmax(fmaxf(fmaxf(z[e][0], z[e][1]), fmaxf(z[e][2], z[e][3])));
+            float ex[4], sum = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { ex[u] = (lane + 32 * u < b2) ? __expf(z[e][u] - mx) : 0.f; sum += ex[u]; }
+            sum = wsum(sum);
+            const float lse = mx + __logf(sum), inv = 1.f / sum;
+            float c = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int l = lane + 32 * u;
+                if (l < b2) {
+                    const float r = ex[u] * inv;
+                    rs_[e * kD + l] = r;
+                    c += r * (z[e][u] - lse);
+                }
+            }
+            cl[e] = wsum(c);
+        }
         __syncwarp();
-        float aa[4] = {0.f, 0.f, 0.f, 0.f}, yy[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t a01[2] = {0, 0}, a23[2] = {0, 0}, y01[2] = {0, 0}, y23[2] = {0, 0};
+#pragma unroll 2
         for (int l = 0; l < b2; ++l) {
-            const float r = rs_[l];
             const float2 k0 = bf2(Ks[l * (kKs / 2) + lane]), k1 = bf2(Ks[l * (kKs / 2) + 32 + lane]);
             const float2 v0 = bf2(Vs[l * (kKs / 2) + lane]), v1 = bf2(Vs[l * (kKs / 2) + 32 + lane]);
-            aa[0] = fmaf(r, k0.x, aa[0]); aa[1] = fmaf(r, k0.y, aa[1]);
-            aa[2] = fmaf(r, k1.x, aa[2]); aa[3] = fmaf(r, k1.y, aa[3]);
-            yy[0] = fmaf(r, v0.x, yy[0]); yy[1] = fmaf(r, v0.y, yy[1]);
-            yy[2] = fmaf(r, v1.x, yy[2]); yy[3] = fmaf(r, v1.y, yy[3]);
+            const uint64_t k01 = f2_pack(k0.x, k0.y), k23 = f2_pack(k1.x, k1.y);
+            const uint64_t v01 = f2_pack(v0.x, v0.y), v23 = f2_pack(v1.x, v1.y);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float r = rs_[e * kD + l];
+                const uint64_t r2 = f2_pack(r, r);
+                a01[e] = f2_fma(r2, k01, a01[e]); a23[e] = f2_fma(r2, k23, a23[e]);
+                y01[e] = f2_fma(r2, v01, y01[e]); y23[e] = f2_fma(r2, v23, y23[e]);
+            }
         }
-        const int64_t slab = ((int64_t)bhl * p.A + a) * b2 + j;
-        const int64_t o = (slab * p.n_keys + n) * kD;
-        *reinterpret_cast<float2*>(p.aL + o + 2 * lane) = make_float2(aa[0] * p.rs, aa[1] * p.rs);
-        *reinterpret_cast<float2*>(p.aL + o + 64 + 2 * lane) = make_float2(aa[2] * p.rs, aa[3] * p.rs);
-        *reinterpret_cast<float2*>(p.Y + o + 2 * lane) = make_float2(yy[0], yy[1]);
-        *reinterpret_cast<float2*>(p.Y + o + 64 + 2 * lane) = make_float2(yy[2], yy[3]);
-        if (lane == 0) p.cL[slab * p.n_keys + n] = cl;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            if (e == 0 || two) {
+                float a0, a1, a2, a3, y0, y1, y2, y3;
+                f2_unpack(a01[e], a0, a1); f2_unpack(a23[e], a2, a3);
+                f2_unpack(y01[e], y0, y1); f2_unpack(y23[e], y2, y3);
+                const int64_t o = out_at[e];
+                *reinterpret_cast<float2*>(p.aL + o + 2 * lane) = make_float2(a0 * p.rs, a1 * p.rs);
+                *reinterpret_cast<float2*>(p.aL + o + 64 + 2 * lane) = make_float2(a2 * p.rs, a3 * p.rs);
+                *reinterpret_cast<float2*>(p.Y + o + 2 * lane) = make_float2(y0, y1);
+                *reinterpret_cast<float2*>(p.Y + o + 64 + 2 * lane) = make_float2(y2, y3);
+                if (lane == 0) p.cL[cl_at[e]] = cl[e];
+            }
+        }
     }
 }
 
@@ -646,7 +676,7 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
 
     const int T = blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16);
     const int LT = blk.b2 <= 64 ? 16 : 32;
-    const size_t smem_fwd = (size_t)2 * kv_tile_words(blk.b2) * 4 + 2 * 8 * kD * sizeof(float);
+    const size_t smem_fwd = (size_t)2 * kv_tile_words(blk.b2) * 4 + 2 * 8 * 2 * kD * sizeof(float);
     const size_t smem_col = ((size_t)2 * 8 * T * kFs + 2 * kTileN * kFs + 2 * 8 * T * (kTileN + 1) + kTileN) * sizeof(float);
     const size_t smem_row = (size_t)2 * kv_tile_words(blk.b2) * 4 +
                             ((size_t)3 * kRowBatch * kD + 2 * kRowBatch * 4 * LT) * sizeof(float);
