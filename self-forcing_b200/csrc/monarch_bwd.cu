@@ -249,12 +249,12 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
         *reinterpret_cast<float4*>(dos + i * kFs + c * 4) = d4;
     }
 
-    float m[T], ls[T], delta[T], dq[T][4];
+    float m[T], ls[T], delta[T];
+    uint64_t dq[T][2];                                 // packed: head-dim elements (lane, lane + 32), (lane + 64, lane + 96)
 #pragma unroll
     for (int t = 0; t < T; ++t) {
         m[t] = -INFINITY; ls[t] = 0.f; delta[t] = 0.f;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) dq[t][u] = 0.f;
+        dq[t][0] = 0; dq[t][1] = 0;
     }
 
     for (int pass = 0; pass < 2; ++pass) {
@@ -276,25 +276,26 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             // logits (and dP = dOut_i . Y_n) for key `lane`, rows warp + 8 t
             const bool valid = t0 + lane < n_seen;
             float s[T], dp[T];
-#pragma unroll
-            for (int t = 0; t < T; ++t) { s[t] = 0.f; dp[t] = 0.f; }
             {
+                uint64_t s2[T], dp2[T];                               // packed (even d, odd d) partial sums
+#pragma unroll
+                for (int t = 0; t < T; ++t) { s2[t] = 0; dp2[t] = 0; }
                 const float* ar = aLs + lane * kFs;
                 const float* yr = Ys + lane * kFs;
 #pragma unroll 2
                 for (int d = 0; d < kD; d += 4) {
-                    const float4 av = *reinterpret_cast<const float4*>(ar + d);
-                    const float4 yv = *reinterpret_cast<const float4*>(yr + d);
+                    const ulonglong2 av = *reinterpret_cast<const ulonglong2*>(ar + d);
+                    const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yr + d);
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
-                        const float4 qv = *reinterpret_cast<const float4*>(qs + (warp + 8 * t) * kFs + d);
-                        const float4 ov = *reinterpret_cast<const float4*>(dos + (warp + 8 * t) * kFs + d);
-                        s[t] = fmaf(qv.x, av.x, s[t]); s[t] = fmaf(qv.y, av.y, s[t]);
-                        s[t] = fmaf(qv.z, av.z, s[t]); s[t] = fmaf(qv.w, av.w, s[t]);
-                        dp[t] = fmaf(ov.x, yv.x, dp[t]); dp[t] = fmaf(ov.y, yv.y, dp[t]);
-                        dp[t] = fmaf(ov.z, yv.z, dp[t]); dp[t] = fmaf(ov.w, yv.w, dp[t]);
+                        const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qs + (warp + 8 * t) * kFs + d);
+                        const ulonglong2 ov = *reinterpret_cast<const ulonglong2*>(dos + (warp + 8 * t) * kFs + d);
+                        s2[t] = f2_fma(qv.x, av.x, s2[t]); s2[t] = f2_fma(qv.y, av.y, s2[t]);
+                        dp2[t] = f2_fma(ov.x, yv.x, dp2[t]); dp2[t] = f2_fma(ov.y, yv.y, dp2[t]);
                     }
                 }
+#pragma unroll
+                for (int t = 0; t < T; ++t) { s[t] = f2_hsum(s2[t]); dp[t] = f2_hsum(dp2[t]); }
             }
             const float cl = cls[lane];
 #pragma unroll
@@ -323,46 +324,47 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             __syncthreads();
             // dq^_i += sum_n ds[i][n] aL_n
             for (int n = 0; n < kTileN; ++n) {
-                float av[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) av[u] = aLs[n * kFs + lane + 32 * u];
+                const float* ar = aLs + n * kFs + lane;
+                const uint64_t a01 = f2_pack(ar[0], ar[32]), a23 = f2_pack(ar[64], ar[96]);
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
                     const float ds = sDS[(warp + 8 * t) * (kTileN + 1) + n];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) dq[t][u] = fmaf(ds, av[u], dq[t][u]);
+                    const uint64_t ds2 = f2_pack(ds, ds);
+                    dq[t][0] = f2_fma(ds2, a01, dq[t][0]);
+                    dq[t][1] = f2_fma(ds2, a23, dq[t][1]);
                 }
             }
             // daL_n = sum_i ds q^_i, dY_n = sum_i P dOut_i for keys warp + 8 v; written over aL / Y
             {
-                float ga[4][4], gy[4][4];
+                uint64_t ga[4][2], gy[4][2];                       // packed like dq
 #pragma unroll
-                for (int v = 0; v < 4; ++v)
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) { ga[v][u] = 0.f; gy[v][u] = 0.f; }
+                for (int v = 0; v < 4; ++v) { ga[v][0] = ga[v][1] = 0; gy[v][0] = gy[v][1] = 0; }
+#pragma unroll 2
                 for (int i = 0; i < b1; ++i) {
-                    float qv[4], dv[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) { qv[u] = qs[i * kFs + lane + 32 * u]; dv[u] = dos[i * kFs + lane + 32 * u]; }
+                    const float* qr = qs + i * kFs + lane;
+                    const float* dr = dos + i * kFs + lane;
+                    const uint64_t q01 = f2_pack(qr[0], qr[32]), q23 = f2_pack(qr[64], qr[96]);
+                    const uint64_t d01 = f2_pack(dr[0], dr[32]), d23 = f2_pack(dr[64], dr[96]);
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         const float ds = sDS[i * (kTileN + 1) + warp + 8 * v];
                         const float pr = sP[i * (kTileN + 1) + warp + 8 * v];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            ga[v][u] = fmaf(ds, qv[u], ga[v][u]);
-                            gy[v][u] = fmaf(pr, dv[u], gy[v][u]);
-                        }
+                        const uint64_t ds2 = f2_pack(ds, ds), pr2 = f2_pack(pr, pr);
+                        ga[v][0] = f2_fma(ds2, q01, ga[v][0]); ga[v][1] = f2_fma(ds2, q23, ga[v][1]);
+                        gy[v][0] = f2_fma(pr2, d01, gy[v][0]); gy[v][1] = f2_fma(pr2, d23, gy[v][1]);
                     }
                 }
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const int n = t0 + warp + 8 * v;
                     if (n < n_seen) {
+                        float a[4], y[4];
+                        f2_unpack(ga[v][0], a[0], a[1]); f2_unpack(ga[v][1], a[2], a[3]);
+                        f2_unpack(gy[v][0], y[0], y[1]); f2_unpack(gy[v][1], y[2], y[3]);
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            g_aL[(int64_t)n * kD + lane + 32 * u] = ga[v][u];
-                            g_Y[(int64_t)n * kD + lane + 32 * u] = gy[v][u];
+                            g_aL[(int64_t)n * kD + lane + 32 * u] = a[u];
+                            g_Y[(int64_t)n * kD + lane + 32 * u] = y[u];
                         }
                     }
                 }
@@ -387,8 +389,11 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
         const int i = warp + 8 * t;
         if (i < b1) {
             float* o = p.dq + (((int64_t)b * p.n_q + p.blk.row_token(a, i) + j) * p.H + hd) * kD;
+            float g[4];
+            f2_unpack(dq[t][0], g[0], g[1]);
+            f2_unpack(dq[t][1], g[2], g[3]);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) o[lane + 32 * u] = dq[t][u] * p.rs;
+            for (int u = 0; u < 4; ++u) o[lane + 32 * u] = g[u] * p.rs;
         }
     }
 }
