@@ -134,27 +134,34 @@ __global__ void __launch_bounds__(256) bwd_row_forward_kernel(const BwdParams p)
         }
         __syncwarp();
         float z[2][4];
+        // key columns lane + 32 u, two at a time: the broadcast reads of the two q^ rows serve both
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int l = lane + 32 * u;
-            z[0][u] = z[1][u] = -INFINITY;
-            if (l < b2) {
-                const uint32_t* kr = Ks + l * (kKs / 2);
-                uint64_t acc[2] = {0, 0};                                  // packed (even d, odd d) partial sums
+        for (int u = 0; u < 4; u += 2) {
+            const int l0 = lane + 32 * u, l1 = l0 + 32;
+            z[0][u] = z[1][u] = z[0][u + 1] = z[1][u + 1] = -INFINITY;
+            if (32 * u < b2) {                                          // warp-uniform
+                const uint32_t* kr0 = Ks + min(l0, b2 - 1) * (kKs / 2);   // lanes past the end recompute the last column
+                const uint32_t* kr1 = Ks + min(l1, b2 - 1) * (kKs / 2);
+                uint64_t acc[2][2] = {{0, 0}, {0, 0}};                  // [row][column], packed (even d, odd d) partial sums
 #pragma unroll 4
                 for (int w = 0; w < kD / 4; ++w) {
-                    const uint2 kw = *reinterpret_cast<const uint2*>(kr + 2 * w);
-                    const float2 k0 = bf2(kw.x), k1 = bf2(kw.y);
-                    const uint64_t k01 = f2_pack(k0.x, k0.y), k23 = f2_pack(k1.x, k1.y);
+                    const uint2 kw0 = *reinterpret_cast<const uint2*>(kr0 + 2 * w);
+                    const uint2 kw1 = *reinterpret_cast<const uint2*>(kr1 + 2 * w);
+                    const float2 a0 = bf2(kw0.x), a1 = bf2(kw0.y), b0 = bf2(kw1.x), b1 = bf2(kw1.y);
+                    const uint64_t ka0 = f2_pack(a0.x, a0.y), ka1 = f2_pack(a1.x, a1.y);
+                    const uint64_t kb0 = f2_pack(b0.x, b0.y), kb1 = f2_pack(b1.x, b1.y);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qs + e * kD + 4 * w);
-                        acc[e] = f2_fma(qv.x, k01, acc[e]);
-                        acc[e] = f2_fma(qv.y, k23, acc[e]);
+                        acc[e][0] = f2_fma(qv.x, ka0, acc[e][0]); acc[e][0] = f2_fma(qv.y, ka1, acc[e][0]);
+                        acc[e][1] = f2_fma(qv.x, kb0, acc[e][1]); acc[e][1] = f2_fma(qv.y, kb1, acc[e][1]);
                     }
                 }
-                z[0][u] = f2_hsum(acc[0]) * p.rs;
-                z[1][u] = f2_hsum(acc[1]) * p.rs;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    if (l0 < b2) z[e][u] = f2_hsum(acc[e][0]) * p.rs;
+                    if (l1 < b2) z[e][u + 1] = f2_hsum(acc[e][1]) * p.rs;
+                }
             }
         }
         float cl[2];
@@ -461,36 +468,60 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
                 }
                 __syncwarp();
                 float z[2][4], ga[2][4];
+                // key columns lane + 32 u, two at a time (u, u + 1): the broadcast reads of the q^ / daL / dY rows serve both
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int l = lane + 32 * u;
-                    z[0][u] = z[1][u] = -INFINITY; ga[0][u] = ga[1][u] = 0.f;
-                    if (l < b2) {
-                        const uint32_t* kr = Ks + l * (kKs / 2);
-                        const uint32_t* vr = Vs + l * (kKs / 2);
-                        uint64_t az[2] = {0, 0}, aa[2] = {0, 0}, ay[2] = {0, 0};      // packed (even d, odd d) partial sums
+                for (int u = 0; u < 4; u += 2) {
+                    const int l0 = lane + 32 * u, l1 = l0 + 32;
+                    z[0][u] = z[1][u] = z[0][u + 1] = z[1][u + 1] = -INFINITY;
+                    ga[0][u] = ga[1][u] = ga[0][u + 1] = ga[1][u + 1] = 0.f;
+                    if (32 * u < b2) {                                  // warp-uniform: some lane has a column in this pair
+                        const int c0 = min(l0, b2 - 1), c1 = min(l1, b2 - 1);          // lanes past the end recompute the last column
+                        const uint32_t* kr0 = Ks + c0 * (kKs / 2);
+                        const uint32_t* vr0 = Vs + c0 * (kKs / 2);
+                        const uint32_t* kr1 = Ks + c1 * (kKs / 2);
+                        const uint32_t* vr1 = Vs + c1 * (kKs / 2);
+                        uint64_t az[2][2] = {{0, 0}, {0, 0}}, aa[2][2] = {{0, 0}, {0, 0}}, ay[2][2] = {{0, 0}, {0, 0}};   // [row][column]
 #pragma unroll 2
                         for (int w = 0; w < kD / 4; ++w) {
-                            const uint2 kw = *reinterpret_cast<const uint2*>(kr + 2 * w);
-                            const uint2 vw = *reinterpret_cast<const uint2*>(vr + 2 * w);
-                            const float2 k0 = bf2(kw.x), k1 = bf2(kw.y), v0 = bf2(vw.x), v1 = bf2(vw.y);
-                            const uint64_t k01 = f2_pack(k0.x, k0.y), k23 = f2_pack(k1.x, k1.y);
-                            const uint64_t v01 = f2_pack(v0.x, v0.y), v23 = f2_pack(v1.x, v1.y);
+                            uint64_t kk[2][2], vv[2][2];                                 // [column][d pair]
+                            {
+                                const uint2 kw = *reinterpret_cast<const uint2*>(kr0 + 2 * w);
+                                const uint2 vw = *reinterpret_cast<const uint2*>(vr0 + 2 * w);
+                                const float2 k0 = bf2(kw.x), k1 = bf2(kw.y), v0 = bf2(vw.x), v1 = bf2(vw.y);
+                                kk[0][0] = f2_pack(k0.x, k0.y); kk[0][1] = f2_pack(k1.x, k1.y);
+                                vv[0][0] = f2_pack(v0.x, v0.y); vv[0][1] = f2_pack(v1.x, v1.y);
+                            }
+                            {
+                                const uint2 kw = *reinterpret_cast<const uint2*>(kr1 + 2 * w);
+                                const uint2 vw = *reinterpret_cast<const uint2*>(vr1 + 2 * w);
+                                const float2 k0 = bf2(kw.x), k1 = bf2(kw.y), v0 = bf2(vw.x), v1 = bf2(vw.y);
+                                kk[1][0] = f2_pack(k0.x, k0.y); kk[1][1] = f2_pack(k1.x, k1.y);
+                                vv[1][0] = f2_pack(v0.x, v0.y); vv[1][1] = f2_pack(v1.x, v1.y);
+                            }
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int slot = warp + 16 * e;
                                 const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qS + slot * kD + 4 * w);
                                 const ulonglong2 av = *reinterpret_cast<const ulonglong2*>(daS + slot * kD + 4 * w);
                                 const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(dyS + slot * kD + 4 * w);
-                                az[e] = f2_fma(qv.x, k01, az[e]); az[e] = f2_fma(qv.y, k23, az[e]);
-                                aa[e] = f2_fma(av.x, k01, aa[e]); aa[e] = f2_fma(av.y, k23, aa[e]);
-                                ay[e] = f2_fma(yv.x, v01, ay[e]); ay[e] = f2_fma(yv.y, v23, ay[e]);
+#pragma unroll
+                                for (int c = 0; c < 2; ++c) {
+                                    az[e][c] = f2_fma(qv.x, kk[c][0], az[e][c]); az[e][c] = f2_fma(qv.y, kk[c][1], az[e][c]);
+                                    aa[e][c] = f2_fma(av.x, kk[c][0], aa[e][c]); aa[e][c] = f2_fma(av.y, kk[c][1], aa[e][c]);
+                                    ay[e][c] = f2_fma(yv.x, vv[c][0], ay[e][c]); ay[e][c] = f2_fma(yv.y, vv[c][1], ay[e][c]);
+                                }
                             }
                         }
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
-                            z[e][u] = f2_hsum(az[e]) * p.rs;
-                            ga[e][u] = f2_hsum(aa[e]) * p.rs + f2_hsum(ay[e]);
+                            if (l0 < b2) {
+                                z[e][u] = f2_hsum(az[e][0]) * p.rs;
+                                ga[e][u] = f2_hsum(aa[e][0]) * p.rs + f2_hsum(ay[e][0]);
+                            }
+                            if (l1 < b2) {
+                                z[e][u + 1] = f2_hsum(az[e][1]) * p.rs;
+                                ga[e][u + 1] = f2_hsum(aa[e][1]) * p.rs + f2_hsum(ay[e][1]);
+                            }
                         }
                     }
                 }
