@@ -14,7 +14,9 @@
 //                               place, tile by tile), dcL_n = -sum_i ds
 //   3. bwd_row_kernel           per block row k, looping over the cached groups f: per unit
 //                               dR_l = daL.k^_l + dY.V_l + dcL (ln R_l + 1), dz = R (dR - sum R dR),
-//                               dQ[a,k,j] += scale sum_l dz_l K_l (this CTA owns those rows: no atomics),
+//                               dQ[a,k,j] += scale sum_l dz_l K_l (the two CTAs of a block row, one per half of
+//                               the cached groups, own those rows in dq and in a second buffer merged afterwards:
+//                               no atomics),
 //                               dK[f,k,l] = sqrt(scale) sum_(a,j) (R_l daL + dz_l q^), dV[f,k,l] = sum_(a,j) R_l dY
 // The kernels are plain fp32 FMA code staged through shared memory: correct and deterministic, not yet on
 // the tensor cores.
@@ -44,6 +46,7 @@ __host__ __device__ inline int kv_tile_words(int b2) { return (b2 * (kKs / 2) + 
 struct BwdParams {
     const bf16 *q, *k, *v, *dout;
     float* dq;
+    float* dq2;                    // scratch like dq: the share of the second half of the cached groups (row kernel)
     bf16 *dk, *dv;
     float *aL, *Y, *cL, *dcL;      // scratch; aL / Y hold daL / dY after the column kernel
     int64_t q_bs, kv_bs;           // batch strides of q and of the cache, in elements
@@ -428,7 +431,11 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
     const int64_t tok = (int64_t)p.H * kD;
     const int n_rows = p.A * b2;
 
-    for (int f = 0; f < p.F; ++f) {
+    // blockIdx.z halves the cached groups; the second half adds up its dQ share in dq2 (merged afterwards)
+    const int f_half = (p.F + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int f_begin = blockIdx.z * f_half, f_end = min(p.F, f_begin + f_half);
+    float* const dq_out = blockIdx.z == 0 ? p.dq : p.dq2;
+    for (int f = f_begin; f < f_end; ++f) {
         const int n = f * p.b1 + k;
         const int64_t kv_off = (int64_t)b * p.kv_bs + ((int64_t)n * b2) * tok + hd * kD;
         __syncthreads();                                             // the previous group's readers are done
@@ -574,8 +581,12 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
                         float d0, d1, d2, d3;
                         f2_unpack(dq01[e], d0, d1);
                         f2_unpack(dq23[e], d2, d3);
-                        float* g = p.dq + (((int64_t)b * p.n_q + t_nat[e]) * p.H + hd) * kD;
-                        float2 g0 = *reinterpret_cast<float2*>(g + 2 * lane), g1 = *reinterpret_cast<float2*>(g + 64 + 2 * lane);
+                        float* g = dq_out + (((int64_t)b * p.n_q + t_nat[e]) * p.H + hd) * kD;
+                        float2 g0 = make_float2(0.f, 0.f), g1 = g0;
+                        if (blockIdx.z == 0 || f > f_begin) {            // dq2 starts from nothing
+                            g0 = *reinterpret_cast<float2*>(g + 2 * lane);
+                            g1 = *reinterpret_cast<float2*>(g + 64 + 2 * lane);
+                        }
                         g0.x += p.scale * d0; g0.y += p.scale * d1;
                         g1.x += p.scale * d2; g1.y += p.scale * d3;
                         *reinterpret_cast<float2*>(g + 2 * lane) = g0;
@@ -626,6 +637,16 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
 }  // namespace
 
 namespace {
+// dq += dq2 for the heads of one slice.  grid (n_q, slice of batch*head), 32 threads: one token row of one head.
+__global__ void bwd_merge_dq_kernel(const BwdParams p) {
+    const int bh = p.bh0 + blockIdx.y, b = bh / p.H, hd = bh - b * p.H;
+    const int64_t o = (((int64_t)b * p.n_q + blockIdx.x) * p.H + hd) * kD + threadIdx.x * 4;
+    float4 a = *reinterpret_cast<float4*>(p.dq + o);
+    const float4 c = *reinterpret_cast<const float4*>(p.dq2 + o);
+    a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+    *reinterpret_cast<float4*>(p.dq + o) = a;
+}
+
 constexpr size_t kDefaultBwdBudget = (size_t)2 << 30;     // scratch per slice of (batch, head) pairs
 
 inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -633,7 +654,7 @@ inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 struct BwdPlan {
     Blocking blk;
     int A, F, n_keys, nbh;
-    size_t off_aL, off_Y, off_cL, off_dcL, total;
+    size_t off_aL, off_Y, off_cL, off_dcL, off_dq2, total;
 };
 
 int make_bwd_plan(BwdPlan* pl, int B, int H, int D, int n_q, int n_kv, int f_tied, int h_reduce, int w_reduce, int h,
@@ -658,6 +679,7 @@ int make_bwd_plan(BwdPlan* pl, int B, int H, int D, int n_q, int n_kv, int f_tie
     pl->off_Y = o; o = up256(o + units * kHeadDim * sizeof(float));
     pl->off_cL = o; o = up256(o + units * sizeof(float));
     pl->off_dcL = o; o = up256(o + units * sizeof(float));
+    pl->off_dq2 = o; o = up256(o + (size_t)B * n_q * H * kHeadDim * sizeof(float));
     pl->total = o;
     return SFM_OK;
 }
@@ -703,6 +725,7 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     unsigned char* ws = (unsigned char*)workspace;
     p.aL = (float*)(ws + pl.off_aL); p.Y = (float*)(ws + pl.off_Y);
     p.cL = (float*)(ws + pl.off_cL); p.dcL = (float*)(ws + pl.off_dcL);
+    p.dq2 = (float*)(ws + pl.off_dq2);
     p.q_bs = q_batch_stride; p.kv_bs = kv_batch_stride;
     p.H = H; p.A = pl.A; p.F = pl.F; p.b1 = blk.b1; p.b2 = blk.b2; p.n_keys = pl.n_keys; p.n_q = n_q;
     p.g0 = kv_group_begin; p.g1 = kv_group_end;
@@ -740,9 +763,11 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
         }
         {
             LaunchScope scope(kClsBackward, s);
-            const dim3 grid(blk.b1, nbh);
+            const int halves = pl.F >= 2 ? 2 : 1;       // 2 x b1 x heads CTAs fill the SMs' rounds more evenly
+            const dim3 grid(blk.b1, nbh, halves);
             if (LT == 16) bwd_row_kernel<16><<<grid, 512, smem_row, s>>>(p);
             else bwd_row_kernel<32><<<grid, 512, smem_row, s>>>(p);
+            if (halves == 2) bwd_merge_dq_kernel<<<dim3(n_q, nbh), 32, 0, s>>>(p);
         }
     }
     return cudaGetLastError() == cudaSuccess ? SFM_OK : SFM_ERR_UNSUPPORTED;
