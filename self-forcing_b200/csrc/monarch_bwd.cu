@@ -37,6 +37,7 @@ using bf16 = __nv_bfloat16;
 constexpr int kD = kHeadDim;
 constexpr int kKs = kD + 4;        // bf16 row stride of a K / V tile in shared memory (66 words: conflict-free 8-byte loads by row)
 constexpr int kFs = kD + 4;        // fp32 row stride of the column kernel's tiles: 16-byte rows, conflict-free float4 by row
+constexpr int kQs = kD;             // fp32 row stride of its q^ / dOut rows (read as broadcasts or by consecutive lanes)
 constexpr int kTileN = 32;         // keys per tile of the column kernel
 constexpr int kRowBatch = 32;      // unit rows per batch of the row kernel
 
@@ -229,13 +230,13 @@ template <int T>
 __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int kRows = 8 * T;
-    float* qs = reinterpret_cast<float*>(smem);        // [kRows][kFs]   q^ rows (zero beyond b1)
-    float* dos = qs + kRows * kFs;                     // [kRows][kFs]   dOut rows
-    float* aLs = dos + kRows * kFs;                    // [kTileN][kFs]
+    float* qs = reinterpret_cast<float*>(smem);        // [kRows][kQs]   q^ rows (zero beyond b1)
+    float* dos = qs + kRows * kQs;                     // [kRows][kQs]   dOut rows
+    float* aLs = dos + kRows * kQs;                    // [kTileN][kFs]
     float* Ys = aLs + kTileN * kFs;                    // [kTileN][kFs]
-    float* sP = Ys + kTileN * kFs;                     // [kRows][kTileN + 1]
-    float* sDS = sP + kRows * (kTileN + 1);            // [kRows][kTileN + 1]
-    float* cls = sDS + kRows * (kTileN + 1);           // [kTileN]
+    float* sP = Ys + kTileN * kFs;                     // [kRows][kTileN]
+    float* sDS = sP + kRows * kTileN;            // [kRows][kTileN]
+    float* cls = sDS + kRows * kTileN;           // [kTileN]
     const int b1 = p.b1, b2 = p.b2, a = blockIdx.x / b2, j = blockIdx.x - a * b2;
     const int bhl = blockIdx.y, bh = p.bh0 + bhl, b = bh / p.H, hd = bh - b * p.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -255,8 +256,8 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             q4 = ld4(p.q + (int64_t)b * p.q_bs + t * tok + hd * kD + c * 4);
             d4 = ld4(p.dout + ((int64_t)b * p.n_q + t) * tok + hd * kD + c * 4);
         }
-        *reinterpret_cast<float4*>(qs + i * kFs + c * 4) = make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
-        *reinterpret_cast<float4*>(dos + i * kFs + c * 4) = d4;
+        *reinterpret_cast<float4*>(qs + i * kQs + c * 4) = make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
+        *reinterpret_cast<float4*>(dos + i * kQs + c * 4) = d4;
     }
 
     float m[T], ls[T], delta[T];
@@ -298,8 +299,8 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
                     const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yr + d);
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
-                        const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qs + (warp + 8 * t) * kFs + d);
-                        const ulonglong2 ov = *reinterpret_cast<const ulonglong2*>(dos + (warp + 8 * t) * kFs + d);
+                        const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qs + (warp + 8 * t) * kQs + d);
+                        const ulonglong2 ov = *reinterpret_cast<const ulonglong2*>(dos + (warp + 8 * t) * kQs + d);
                         s2[t] = f2_fma(qv.x, av.x, s2[t]); s2[t] = f2_fma(qv.y, av.y, s2[t]);
                         dp2[t] = f2_fma(ov.x, yv.x, dp2[t]); dp2[t] = f2_fma(ov.y, yv.y, dp2[t]);
                     }
@@ -328,8 +329,8 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
 #pragma unroll
             for (int t = 0; t < T; ++t) {
                 const float pr = valid ? __expf(s[t] - m[t]) : 0.f;          // m holds the log-sum-exp now
-                sP[(warp + 8 * t) * (kTileN + 1) + lane] = pr;
-                sDS[(warp + 8 * t) * (kTileN + 1) + lane] = pr * (dp[t] - delta[t]);
+                sP[(warp + 8 * t) * kTileN + lane] = pr;
+                sDS[(warp + 8 * t) * kTileN + lane] = pr * (dp[t] - delta[t]);
             }
             __syncthreads();
             // dq^_i += sum_n ds[i][n] aL_n
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
                 const uint64_t a01 = f2_pack(ar[0], ar[32]), a23 = f2_pack(ar[64], ar[96]);
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
-                    const float ds = sDS[(warp + 8 * t) * (kTileN + 1) + n];
+                    const float ds = sDS[(warp + 8 * t) * kTileN + n];
                     const uint64_t ds2 = f2_pack(ds, ds);
                     dq[t][0] = f2_fma(ds2, a01, dq[t][0]);
                     dq[t][1] = f2_fma(ds2, a23, dq[t][1]);
@@ -351,14 +352,14 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
                 for (int v = 0; v < 4; ++v) { ga[v][0] = ga[v][1] = 0; gy[v][0] = gy[v][1] = 0; }
 #pragma unroll 2
                 for (int i = 0; i < b1; ++i) {
-                    const float* qr = qs + i * kFs + lane;
-                    const float* dr = dos + i * kFs + lane;
+                    const float* qr = qs + i * kQs + lane;
+                    const float* dr = dos + i * kQs + lane;
                     const uint64_t q01 = f2_pack(qr[0], qr[32]), q23 = f2_pack(qr[64], qr[96]);
                     const uint64_t d01 = f2_pack(dr[0], dr[32]), d23 = f2_pack(dr[64], dr[96]);
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
-                        const float ds = sDS[i * (kTileN + 1) + warp + 8 * v];
-                        const float pr = sP[i * (kTileN + 1) + warp + 8 * v];
+                        const float ds = sDS[i * kTileN + warp + 8 * v];
+                        const float pr = sP[i * kTileN + warp + 8 * v];
                         const uint64_t ds2 = f2_pack(ds, ds), pr2 = f2_pack(pr, pr);
                         ga[v][0] = f2_fma(ds2, q01, ga[v][0]); ga[v][1] = f2_fma(ds2, q23, ga[v][1]);
                         gy[v][0] = f2_fma(pr2, d01, gy[v][0]); gy[v][1] = f2_fma(pr2, d23, gy[v][1]);
@@ -381,7 +382,7 @@ __global__ void __launch_bounds__(256) bwd_col_kernel(const BwdParams p) {
             }
             if (tid < kTileN && t0 + tid < n_seen) {
                 float acc = 0.f;
-                for (int i = 0; i < b1; ++i) acc += sDS[i * (kTileN + 1) + tid];
+                for (int i = 0; i < b1; ++i) acc += sDS[i * kTileN + tid];
                 g_dcL[t0 + tid] = -acc;
             }
         }
@@ -736,7 +737,7 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     const int T = blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16);
     const int LT = blk.b2 <= 64 ? 16 : 32;
     const size_t smem_fwd = (size_t)2 * kv_tile_words(blk.b2) * 4 + 2 * 8 * 2 * kD * sizeof(float);
-    const size_t smem_col = ((size_t)2 * 8 * T * kFs + 2 * kTileN * kFs + 2 * 8 * T * (kTileN + 1) + kTileN) * sizeof(float);
+    const size_t smem_col = ((size_t)2 * 8 * T * kQs + 2 * kTileN * kFs + 2 * 8 * T * kTileN + kTileN) * sizeof(float);
     const size_t smem_row = (size_t)2 * kv_tile_words(blk.b2) * 4 +
                             ((size_t)3 * kRowBatch * kD + 2 * kRowBatch * 4 * LT) * sizeof(float);
     int bad = opt_in_smem(bwd_row_forward_kernel, smem_fwd);
