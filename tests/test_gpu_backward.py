@@ -186,3 +186,25 @@ def test_nocache_autograd(sfb, ci, causal_frames):
     grad_close(qg.grad, q32.grad, 1e-2, "q.grad")
     grad_close(kg.grad, k32.grad, 1e-2, "k.grad")
     grad_close(vg.grad, v32.grad, 1e-2, "v.grad")
+
+
+def test_backward_properties_full_size(sfb):
+    """Headline size (one 3-frame chunk against 7 cached chunks, 12 heads), where the oracle is too slow:
+    the output is linear in V, so <dOut, out> = <dV, V> (checked with dOut = out, against the forward kernels'
+    own output); doubling dOut doubles every gradient bit for bit; two runs agree bit for bit."""
+    g = torch.Generator(device="cpu").manual_seed(8700)
+    H, n_q, n_kv = 12, 4680, 7 * 4680
+    mk = lambda n: torch.randn(1, n, H, 128, generator=g).to(torch.bfloat16).cuda()
+    q, kc, vc = mk(n_q), mk(n_kv), mk(n_kv)
+    blocking = (1, 1, 1, 30, 52)
+    out = sfb.ops.monarch_attention_on_cache(q, kc, vc, *blocking)
+    dq, dk, dv = sfb.monarch_attn_with_kv_cache_backward(q, kc, vc, out, *blocking)
+    dq_b, dk_b, dv_b = sfb.monarch_attn_with_kv_cache_backward(q, kc, vc, out, *blocking)
+    dq2, dk2, dv2 = sfb.monarch_attn_with_kv_cache_backward(q, kc, vc, out * 2, *blocking)
+    torch.cuda.synchronize()
+    assert torch.isfinite(dq).all() and torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
+    assert torch.equal(dq, dq_b) and torch.equal(dk, dk_b) and torch.equal(dv, dv_b)
+    assert torch.equal(dq2, dq * 2) and torch.equal(dk2, dk * 2) and torch.equal(dv2, dv * 2)
+    lhs = (out.double() ** 2).sum().item()
+    rhs = (dv.double() * vc.double()).sum().item()
+    assert abs(lhs - rhs) <= 1e-2 * lhs, (lhs, rhs)
