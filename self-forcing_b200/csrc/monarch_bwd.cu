@@ -734,15 +734,16 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     p.scale = sm_scale; p.rs = sqrtf(sm_scale);
     p.blk = blk;
 
-    const int T = blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16);
+    const int T = blk.b1 <= 16 ? 2 : (blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16));
     const int LT = blk.b2 <= 64 ? 16 : 32;
     const size_t smem_fwd = (size_t)2 * kv_tile_words(blk.b2) * 4 + 2 * 8 * 2 * kD * sizeof(float);
     const size_t smem_col = ((size_t)2 * 8 * T * kQs + 2 * kTileN * kFs + 2 * 8 * T * kTileN + kTileN) * sizeof(float);
     const size_t smem_row = (size_t)2 * kv_tile_words(blk.b2) * 4 +
                             ((size_t)3 * kRowBatch * kD + 2 * kRowBatch * 4 * LT) * sizeof(float);
     int bad = opt_in_smem(bwd_row_forward_kernel, smem_fwd);
-    bad |= T == 4 ? opt_in_smem(bwd_col_kernel<4>, smem_col)
-                  : (T == 8 ? opt_in_smem(bwd_col_kernel<8>, smem_col) : opt_in_smem(bwd_col_kernel<16>, smem_col));
+    bad |= T == 2 ? opt_in_smem(bwd_col_kernel<2>, smem_col)
+                  : (T == 4 ? opt_in_smem(bwd_col_kernel<4>, smem_col)
+                            : (T == 8 ? opt_in_smem(bwd_col_kernel<8>, smem_col) : opt_in_smem(bwd_col_kernel<16>, smem_col)));
     bad |= LT == 16 ? opt_in_smem(bwd_row_kernel<16>, smem_row) : opt_in_smem(bwd_row_kernel<32>, smem_row);
     if (bad) return SFM_ERR_UNSUPPORTED;
 
@@ -758,7 +759,8 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
         {
             LaunchScope scope(kClsBackward, s);
             const dim3 grid(pl.A * blk.b2, nbh);
-            if (T == 4) bwd_col_kernel<4><<<grid, 256, smem_col, s>>>(p);
+            if (T == 2) bwd_col_kernel<2><<<grid, 256, smem_col, s>>>(p);
+            else if (T == 4) bwd_col_kernel<4><<<grid, 256, smem_col, s>>>(p);
             else if (T == 8) bwd_col_kernel<8><<<grid, 256, smem_col, s>>>(p);
             else bwd_col_kernel<16><<<grid, 256, smem_col, s>>>(p);
         }
