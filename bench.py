@@ -293,6 +293,73 @@ def run_rollout(args, sfb, rank, world, device, barrier):
             "clocks": clocks}))
 
 
+def run_model(args, rank, world, device, barrier):
+    """BASELINE's full-model configurations: the reference's own CausalWanModel, WanDiffusionWrapper and
+    CausalInferencePipeline, imported unmodified from a staged checkout (baseline/stage_reference.py), with
+    random-init bf16 weights, a random 512x4096 text context and seeded latent noise; 21 frames in 7 chunks
+    of 3, 4 denoising steps plus the clean-context pass per chunk.  --attention selects what the model's
+    self-attention calls: "ours" = this package behind wan.modules.monarch_attn / wan.modules.attention,
+    "patched" = additionally the fused layer path in place of the cache branch of
+    CausalWanSelfAttention.forward, "reference" = the reference's Triton / flash-attn operators.  Times are
+    the pipeline's own CUDA events (inference(profile=True)); every rank generates its own videos."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_harness as rh
+    base = {"metric": "wan_latent_frames_per_s", "unit": "latent frames/s (4-step causal rollout, whole DiT)",
+            "n_gpus": world, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random-init weights, random text context, seeded noise)"}
+    root = rh.reference_root()
+    if root is None:
+        if rank == 0:
+            print(json.dumps({**base, "unavailable": "reference sources not staged: run baseline/stage_reference.py "
+                                                     "with SF_REFERENCE_ROOT pointing at a Self-Forcing checkout"}))
+        return
+    rh.prepare_imports(root, attention="reference" if args.attention == "reference" else "ours")
+    overrides = {"num_layers": args.layers} if args.layers else {}
+    pipe = rh.build_pipeline(args.model, args.blocking, device=device, dense_init=args.dense_init,
+                             num_iters=args.num_iters, seed=rank, **overrides)
+    if args.attention == "patched":
+        import self_forcing_b200 as sfb
+        from self_forcing_b200.install import patch_self_attention_forward
+        from wan.modules.causal_model import CausalWanSelfAttention
+        patch_self_attention_forward(CausalWanSelfAttention)
+    from self_forcing_b200 import _lib
+    lib = _lib.load() if args.attention != "reference" else None
+    for _ in range(max(1, min(args.warmup, 2))):
+        rh.run_rollout(pipe, batch=args.batch, device=device, seed=10 + rank)
+    torch.cuda.synchronize()
+    barrier()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    n0 = lib.sfm_launch_count() if lib else 0
+    diff_ms, block_ms = [], []
+    steps = max(1, args.steps)
+    for i in range(steps):
+        _, prof = rh.run_rollout(pipe, batch=args.batch, device=device, seed=20 + rank + i)
+        diff_ms.append(prof["diffusion_ms"])
+        block_ms.append(prof["block_ms"])
+    launches = (lib.sfm_launch_count() - n0) // steps if lib else 0
+    clocks = sampler.stop()
+    barrier()
+    ms = statistics.median(diff_ms)
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    if rank == 0:
+        chunks = [statistics.median(b[i] for b in block_ms) for i in range(len(block_ms[0]))]
+        shape = rh.MODEL_SHAPES[args.model]
+        print(json.dumps({**base, "value": 21 * args.batch * world / (ms * 1e-3), "steps": steps,
+                          "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms, "ms_per_chunk": chunks,
+                          "config": {"workload": f"causal Wan-{args.model.upper()} DiT ({shape['num_layers'] if not args.layers else args.layers} blocks, dim "
+                                                 f"{shape['dim']}, {shape['num_heads']} heads, FFN {shape['ffn_dim']}), 21x60x104 latent in 7 "
+                                                 f"chunks of 3 frames, timesteps [1000, 750, 500, 250] + clean-context pass, "
+                                                 f"{args.blocking} self-attention with KV cache, batch {args.batch} per GPU",
+                                     "attention": args.attention, "blocking": args.blocking, "batch": args.batch,
+                                     "parallelism": f"dp{world} (independent videos per GPU)"},
+                          "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+
+
 def run_backward(args, sfb, rank, world, device, barrier):
     """Forward + backward of the Monarch attention op at the headline shape (one 3-frame chunk against k cached
     chunks, 12 heads): the call a training rollout makes per layer (gradients of q and of the chunk's own keys
@@ -441,6 +508,14 @@ def main():
     ap.add_argument("--dense-init", action="store_true", help="with --rollout: dense attention for the first chunk")
     ap.add_argument("--p2p", action="store_true",
                     help="with --ulysses: the kernels gather / scatter over peer memory instead of the two NCCL all-to-alls")
+    ap.add_argument("--model", default=None, choices=["1.3b", "14b"],
+                    help="time the whole causal DiT rollout through the reference's unmodified model and pipeline code "
+                         "(needs the staged reference sources, see baseline/stage_reference.py) instead of the headline workload")
+    ap.add_argument("--attention", default="ours", choices=["ours", "patched", "reference"],
+                    help="with --model: what the model's self-attention runs on")
+    ap.add_argument("--batch", type=int, default=1, help="with --model: videos per GPU")
+    ap.add_argument("--layers", type=int, default=0, help="with --model: override the number of blocks (0 = the model's)")
+    ap.add_argument("--num-iters", type=int, default=1, help="with --model: MONARCH_ATTN_NUM_ITERS")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -463,6 +538,12 @@ def main():
         barrier = lambda: dist.barrier()
     else:
         barrier = lambda: None
+
+    if args.model:
+        run_model(args, rank, world, device, barrier)
+        if use_dist:
+            dist.destroy_process_group()
+        return
 
     import self_forcing_b200 as sfb
     from self_forcing_b200 import _lib

@@ -150,9 +150,14 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     CUtensorMap maps[6];
     const int rows_per_group = (pl.blk.b2 + 7) & ~7;
     const int n_s = (pl.blk.b2 + 15) & ~15;
-    if (use_tc) {
+    {
+        // Every path starts from a clear status word: the workspace may be recycled memory, and the kernels
+        // without bounded waits (iterative variant, block rows above 128) never write it.
         cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
         if (e != cudaSuccess) return (int)e;
+    }
+    if (use_tc) {
+        cudaError_t e;
         // cL rows are padded to 16 bytes; the pad floats travel with the column step's bulk copies and
         // must act as "key masked": fill the buffer with a huge positive bias (0x7f7f7f7f = 3.4e38).
         e = cudaMemsetAsync(p.cL, 0x7f, (size_t)pl.nbh_chunk * pl.na_chunk * pl.blk.b2 * p.n_keys_c * sizeof(float), stream);

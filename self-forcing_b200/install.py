@@ -63,7 +63,12 @@ def patch_self_attention_forward(cls) -> None:
                 timestep=None, **kw):
         special = getattr(self, "topk", None) is not None or getattr(self, "use_svg", False) or \
             getattr(self, "use_radial_attn", False)
-        if kv_cache is None or special or x.dtype != torch.bfloat16:
+        wq = getattr(self.norm_q, "weight", None)
+        wk = getattr(self.norm_k, "weight", None)
+        # The fused kernel multiplies by bf16 norm weights, as the bf16 module does; a module kept in another
+        # precision (fp32 norm weights promote the reference's product to fp32) stays on the original forward.
+        odd_norm = (wq is None) != (wk is None) or any(w is not None and w.dtype != torch.bfloat16 for w in (wq, wk))
+        if kv_cache is None or special or odd_norm or x.dtype != torch.bfloat16:
             return original(self, x, seq_lens, grid_sizes, freqs, block_mask, kv_cache=kv_cache,
                             current_start=current_start, cache_start=cache_start, timestep=timestep, **kw)
         b, s, n, d = *x.shape[:2], self.num_heads, self.head_dim
@@ -74,18 +79,21 @@ def patch_self_attention_forward(cls) -> None:
         if state is None or state.stale(kv_cache):
             state = layer.KVCache.from_reference(kv_cache)         # reads the two indices once
             kv_cache["_sfm_state"] = state
-        grid = getattr(self, "_sfm_grid", None)
-        if grid is None or grid[0] != int(s):
-            g = [int(t) for t in grid_sizes[0].tolist()]           # once per chunk shape, not per call
-            grid = (int(s), tuple(g))
-            self._sfm_grid = grid
+        if grid_sizes.device.type == "cpu":                        # the model builds it on the host: free to read
+            grid = (int(s), tuple(int(t) for t in grid_sizes[0].tolist()))
+        else:
+            # a device tensor costs a read-back: do it once per tensor, not per call (same token count with
+            # another (rows, columns) split arrives in another tensor)
+            grid = getattr(self, "_sfm_grid", None)
+            key = (int(s), grid_sizes.data_ptr(), grid_sizes._version)
+            if grid is None or grid[2] != key:
+                grid = (int(s), tuple(int(t) for t in grid_sizes[0].tolist()), key)
+                self._sfm_grid = grid
         cfg = layer.LayerConfig(use_framewise=bool(self.use_framewise), h_reduce=int(self.h_reduce),
                                 w_reduce=int(self.w_reduce), num_iters=int(self.num_iters),
                                 disable_monarch=bool(self.disable_monarch), use_dense_init=bool(self.use_dense_init),
                                 local_attn_size=int(self.local_attn_size), sink_size=int(self.sink_size),
                                 max_attention_size=int(self.max_attention_size), eps=float(self.eps))
-        wq = getattr(self.norm_q, "weight", None)
-        wk = getattr(self.norm_k, "weight", None)
         out = layer.self_attention_kv(q, k, v, state, int(current_start), grid[1], cfg, freqs=freqs,
                                       norm_q_weight=wq, norm_k_weight=wk)
         return self.o(out.flatten(2))

@@ -124,6 +124,15 @@ def _rope_table_from_freqs(freqs: Optional[torch.Tensor], device: torch.device) 
     return tab
 
 
+def _mark_written(*tensors) -> None:
+    """The kernels write the caches through raw pointers, which autograd cannot see.  Bumping the version
+    counters makes a later backward that saved one of these tensors fail loudly, as it does after the
+    reference's slice assignment (monarch_attn.py:1230-1231), instead of using overwritten keys."""
+    for t in tensors:
+        if not t.is_inference():                   # inference tensors carry no version counter
+            torch.autograd.graph.increment_version(t)
+
+
 def workspace_bytes(B, H, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, num_iters=1, bridge_budget_bytes=0) -> int:
     return int(_lib.load().sfm_monarch_workspace_bytes(B, H, 128, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w,
                                                        num_iters, bridge_budget_bytes))
@@ -239,11 +248,10 @@ class _MonarchWithKVCacheFn(torch.autograd.Function):
         idx = torch.from_numpy(nat2mon.astype(np.int64)).to(q.device)
         d_new_k = dk[:, lo:lo + end - start].index_select(1, idx)
         d_new_v = dv[:, lo:lo + end - start].index_select(1, idx)
-        d_kc = d_vc = None
-        if want_cache:                                  # the written slots do not depend on the cache's old content
-            d_kc, d_vc = dk.clone(), dv.clone()
-            d_kc[:, start:end] = 0
-            d_vc[:, start:end] = 0
+        # The reference hands back the gradient with respect to the cache CONTENT after its in-place write,
+        # written slot included (monarch_attn.py:1462-1470; its PyTorch restatement retains the gradient of
+        # the cache after the write, :1869-1872), so the same is returned here.
+        d_kc, d_vc = (dk, dv) if want_cache else (None, None)
         return dq, d_new_k, d_new_v, d_kc, d_vc, None, None, None, None, None
 
 
@@ -278,7 +286,9 @@ def monarch_attn_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end
     rotated); caches [B, n_kv, H, 128] bf16, possibly a [:, :n_kv] view of a longer buffer.  Returns
     [B, n_q, H, 128].  When autograd is recording and an input requires a gradient the call goes
     through an autograd function whose backward runs the backward kernels (single pass only);
-    grad_only_new_kv then limits dK / dV to the slots this call wrote."""
+    grad_only_new_kv then limits dK / dV to the slots this call wrote.  As in the reference, the cache
+    gradient is the one with respect to the cache content after the write (the written slot carries the new
+    keys' gradient in Monarch order), and writing the cache again before backward is an error."""
     if (not _no_grad and torch.is_grad_enabled()
             and any(t.requires_grad for t in (q, new_k, new_v, k_cache, v_cache))):
         if num_iters != 1:
@@ -304,6 +314,7 @@ def monarch_attn_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end
                                           _ptr(v_cache), _batch_stride(k_cache), _ptr(None), B, n_new, H, D,
                                           int(start_idx), f_tied, h_reduce, w_reduce, h, w, 0, 1, _stream())
     _lib.check(rc, "sfm_rope_cache_write")
+    _mark_written(k_cache, v_cache)
     return _monarch_fwd(q, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
 
 
@@ -341,6 +352,7 @@ def norm_rope_cache_write(q, k, v, k_cache, v_cache, start_idx, start_frame, f_t
                                       _batch_stride(k_cache), _ptr(tab), B, n, H, D, int(start_idx), f_tied, h_reduce,
                                       w_reduce, h, w, int(start_frame), 1 if monarch_order else 0, _stream())
         _lib.check(rc, "sfm_rope_cache_write")
+    _mark_written(k_cache, v_cache)
     return q_rot
 
 
@@ -367,6 +379,7 @@ def rope_monarch_attn_with_kv_cache(q, k, v, k_cache, v_cache, start_idx, end_id
                                           _batch_stride(k_cache), _ptr(tab), B, n_q, H, D, int(start_idx), f_tied,
                                           h_reduce, w_reduce, h, w, int(start_frame), 1, _stream())
     _lib.check(rc, "sfm_rope_cache_write")
+    _mark_written(k_cache, v_cache)
     return _monarch_fwd(q_rot, k_cache, v_cache, f_tied, h_reduce, w_reduce, h, w, sm_scale, num_iters)
 
 
@@ -406,6 +419,7 @@ def rope_monarch_attn_with_kv_cache_sharded(q_shards, k_shards, v_shards, out_sh
                                          _ptr(tab), B, n_q, H, D, int(start_idx), f_tied, h_reduce, w_reduce, h, w,
                                          int(start_frame), 1, _stream())
     _lib.check(rc, "sfm_rope_cache_write_gather")
+    _mark_written(k_cache, v_cache)
     n_kv = end_idx
     kc, vc = k_cache[:, :n_kv], v_cache[:, :n_kv]
     nbytes = lib.sfm_monarch_workspace_bytes(B, H, D, n_q, n_kv, f_tied, h_reduce, w_reduce, h, w, 1, 0) or 256
@@ -530,6 +544,7 @@ def full_attention_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, e
                                           _ptr(v_cache), _batch_stride(k_cache), _ptr(None), B, n_new, H, D,
                                           int(start_idx), 1, 1, 1, 1, 1, 0, 0, _stream())
     _lib.check(rc, "sfm_rope_cache_write")
+    _mark_written(k_cache, v_cache)
     return attention(q, k_cache, v_cache, softmax_scale=sm_scale)
 
 

@@ -92,3 +92,73 @@ def c1_case():
     chunk = 3 * h * w
     q, k, v = randn(rng, B, chunk, H, D), randn(rng, B, chunk, H, D), randn(rng, B, chunk, H, D)
     return dict(q=q, k=k, v=v, h=h, w=w, chunk=chunk, sm_scale=D ** -0.5)
+
+
+# ---------------------------------------------------------------------------------------------
+# second fixture file (pins_golden.npz): gradients, dense attention, cache bookkeeping
+# ---------------------------------------------------------------------------------------------
+PIN_CHANNEL_STRIDE = 2            # gradient fixtures keep every second head-dim channel (file size)
+
+
+def _bf16_round(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def grad_case(ci: int):
+    """Cache-path gradient case at head_dim 128 (the only size the kernels are built for): B=1, H=2, the
+    last `frames_q` tied frame sets of a `groups` set cache written by the call.  Values are rounded to
+    bf16 so that the reference (fp32 arithmetic) and the kernels (bf16 storage) see the same numbers."""
+    name, ft, hr, wr, h, w = SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(8100 + ci)
+    frames_q, sets = (2, 4) if ft == 1 else (1, 2)
+    tied = ft * h * w
+    n_q, n_kv = frames_q * tied, sets * tied
+    B, H, D = 1, 2, 128
+    mk = lambda n: _bf16_round(randn(rng, B, n, H, D))
+    return dict(name=name, blocking=(ft, hr, wr, h, w), q=mk(n_q), nk=mk(n_q), nv=mk(n_q), kbuf=mk(n_kv + tied),
+                vbuf=mk(n_kv + tied), g=mk(n_q), start=n_kv - n_q, end=n_kv, n_kv=n_kv, sm_scale=D ** -0.5)
+
+
+CAUSAL_GRAD_CASES = [(0, 2), (3, 3)]      # (index into SMALL_BLOCKINGS, frames per causal block)
+
+
+def causal_grad_case(i: int):
+    ci, causal_frames = CAUSAL_GRAD_CASES[i]
+    name, ft, hr, wr, h, w = SMALL_BLOCKINGS[ci]
+    rng = np.random.default_rng(8600 + i)
+    n = 6 * ft * h * w
+    B, H, D = 1, 2, 128
+    mk = lambda: _bf16_round(randn(rng, B, n, H, D))
+    return dict(name=name, blocking=(ft, hr, wr, h, w), q=mk(), k=mk(), v=mk(), g=mk(),
+                block_causal=causal_frames * ft * h * w, sm_scale=D ** -0.5)
+
+
+DENSE_CASES = [(50, 170), (333, 1000)]
+
+
+def dense_case(i: int):
+    """Dense attention: B=1, H=2, D=128, K/V given as a view shorter than their buffer."""
+    n_q, n_kv = DENSE_CASES[i]
+    rng = np.random.default_rng(31 + n_q)
+    mk = lambda n: _bf16_round(randn(rng, 1, n, 2, 128))
+    return dict(q=mk(n_q), kbuf=mk(n_kv + 64), vbuf=mk(n_kv + 64), n_kv=n_kv)
+
+
+# Rollouts replayed through the reference's CausalWanSelfAttention.forward cache branch.  Each scenario:
+# cache size in frames, local_attn_size, sink_size (frames), and the list of (chunk index, repeats) layer
+# calls: a chunk of 3 frames starts at token 3 * 1560 * chunk index and is called `repeats` times (the
+# pipeline rewrites the chunk's slot with every denoising step and once more with the clean context).
+BOOKKEEPING_SCENARIOS = {
+    "global_7chunks": dict(cache_frames=21, local_attn_size=-1, sink_size=0,
+                           calls=[(c, 5) for c in range(7)]),
+    "window9_sink0": dict(cache_frames=9, local_attn_size=9, sink_size=0,
+                          calls=[(c, 2) for c in range(6)]),
+    "window12_sink3": dict(cache_frames=12, local_attn_size=12, sink_size=3,
+                           calls=[(c, 3) for c in range(7)]),
+    # a cache longer than the attention window: no eviction until it is full, but the view starts past 0
+    "window6_cache21": dict(cache_frames=21, local_attn_size=6, sink_size=0,
+                            calls=[(c, 2) for c in range(7)]),
+    "window6_sink1_dense_init": dict(cache_frames=6, local_attn_size=6, sink_size=1,
+                                     calls=[(c, 2) for c in range(5)], dense_init=True),
+}
+BOOKKEEPING_ID_STRIDE = 130       # the cache's token ids are stored every 130 tokens (12 per frame)

@@ -1,9 +1,12 @@
 """Generate the golden fixtures in this directory from the reference's own code.
 
-Run once, in a container that has the reference checkout (default
-``/root/reference``; override with ``SF_REFERENCE_ROOT``):
+Run once, in a container that has the reference checkout, with ``SF_REFERENCE_ROOT`` pointing at it:
 
-    python tests/golden/make_golden.py
+    SF_REFERENCE_ROOT=/path/to/Self-Forcing python tests/golden/make_golden.py [--only-pins]
+
+Two files are written: ``monarch_golden.npz`` (layout maps, RoPE, RMSNorm, forward results) and
+``pins_golden.npz`` (gradients, dense attention, KV-cache bookkeeping); ``--only-pins`` regenerates the
+second one alone.
 
 The reference module ``wan/modules/monarch_attn.py`` cannot be imported without
 a CUDA driver (it asserts on a Triton target at import time), so its
@@ -30,10 +33,13 @@ from einops import rearrange
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
 import cases  # noqa: E402
-REF = Path(os.environ.get("SF_REFERENCE_ROOT", "/root/reference"))
+if not os.environ.get("SF_REFERENCE_ROOT"):
+    sys.exit("set SF_REFERENCE_ROOT to a checkout of the reference project")
+REF = Path(os.environ["SF_REFERENCE_ROOT"])
+ROOT = HERE.parent.parent
 
 
-def _extract(path: Path, names):
+def _extract(path: Path, names, extra=None):
     src = path.read_text()
     tree = ast.parse(src)
     wanted = [n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef)) and n.name in names]
@@ -41,6 +47,7 @@ def _extract(path: Path, names):
     if missing:
         raise RuntimeError(f"not found in {path}: {missing}")
     ns = {"torch": torch, "nn": torch.nn, "rearrange": rearrange, "math": math}
+    ns.update(extra or {})
     code = ast.Module(body=wanted, type_ignores=[])
     exec(compile(code, str(path), "exec"), ns)
     return ns
@@ -182,5 +189,147 @@ def main():
     print(f"wrote {len(out)} arrays, {sz/1e6:.2f} MB")
 
 
+# =============================================================================================
+# pins_golden.npz
+# =============================================================================================
+def gradient_pins(ns, out):
+    """Gradients from the reference's own gradient oracle: autograd through monarch_attn_with_kv_cache_ref
+    (monarch_attn.py:1860-1878), used the way run_kv_cache_test does (:1880-1932): q, new_k, new_v are
+    leaves; the cache tensors are not, and with grad_only_new_kv=False their retained gradient (taken
+    after the in-place write, so it covers the written slot too) is the cache gradient."""
+    for ci in range(len(cases.SMALL_BLOCKINGS)):
+        c = cases.grad_case(ci)
+        ft, hr, wr, h, w = c["blocking"]
+        res = {}
+        for only_new in (False, True):
+            q = c["q"].clone().requires_grad_(True)
+            nk, nv = c["nk"].clone().requires_grad_(True), c["nv"].clone().requires_grad_(True)
+            kc, vc = c["kbuf"][:, :c["n_kv"]].clone(), c["vbuf"][:, :c["n_kv"]].clone()
+            z = ns["monarch_attn_with_kv_cache_ref"](q, kc, vc, nk, nv, c["start"], c["end"], ft, hr, wr, h, w,
+                                                     c["sm_scale"], grad_only_new_kv=only_new)
+            z.backward(c["g"])
+            res[only_new] = dict(z=z.detach(), dq=q.grad, dnk=nk.grad, dnv=nv.grad,
+                                 dkc=None if only_new else kc.grad, dvc=None if only_new else vc.grad)
+        for name in ("z", "dq", "dnk", "dnv"):          # the mode only decides which gradients exist
+            assert torch.equal(res[False][name], res[True][name])
+        key = f"grad_{c['name']}"
+        for name, val in res[False].items():
+            out[f"{key}_{name}"] = val[..., ::cases.PIN_CHANNEL_STRIDE].numpy()
+    for i in range(len(cases.CAUSAL_GRAD_CASES)):
+        c = cases.causal_grad_case(i)
+        ft, hr, wr, h, w = c["blocking"]
+        q, k, v = (c[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+        z = ns["monarch_attn_causal_ref"](q, k, v, ft, hr, wr, h, w, c["block_causal"], c["sm_scale"])
+        z.backward(c["g"])
+        key = f"causalgrad_{c['name']}"
+        cs = cases.PIN_CHANNEL_STRIDE
+        out[key + "_dq"] = q.grad[..., ::cs].numpy()
+        out[key + "_dk"], out[key + "_dv"] = k.grad[..., ::cs].numpy(), v.grad[..., ::cs].numpy()
+
+
+def dense_pins(out):
+    """The reference's dense attention() with its flash-attn branch switched off, i.e. its own SDPA
+    fallback (attention.py:177-187): once in fp32 (the parity target) and once with the default
+    dtype=bfloat16 cast the function applies (recorded for information)."""
+    import warnings
+    ns = _extract(REF / "wan/modules/attention.py", ["attention"],
+                  extra={"FLASH_ATTN_2_AVAILABLE": False, "FLASH_ATTN_3_AVAILABLE": False, "warnings": warnings})
+    for i in range(len(cases.DENSE_CASES)):
+        c = cases.dense_case(i)
+        k, v = c["kbuf"][:, :c["n_kv"]], c["vbuf"][:, :c["n_kv"]]
+        out[f"dense_{i}_fp32"] = ns["attention"](c["q"], k, v, dtype=torch.float32).numpy()
+        out[f"dense_{i}_bf16_bits"] = ns["attention"](c["q"], k, v).contiguous().view(torch.int16).numpy()
+
+
+def bookkeeping_pins(out):
+    """Replays rollouts through the reference's CausalWanSelfAttention.forward (cache branch,
+    causal_model.py:900-1103) on the CPU.  The attention operators are replaced by stand-ins that perform
+    the cache write the real ones do and return zeros; what is recorded is pure index arithmetic: per
+    call the view the operator was given (offset into the cache and length), the slot it wrote, the two
+    end indices the module stored afterwards, and which token sits where in the cache (token ids kept
+    in one element of every cache row, so that the eviction shift is captured as the module performs it)."""
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_harness as rh
+    rh.prepare_imports(REF, attention="ours")
+    import wan.modules.causal_model as cm
+
+    frame = 30 * 52
+    rec = {}
+
+    def view_of(cache_k, view):
+        row = cache_k.stride(1) * cache_k.element_size()
+        off = (view.data_ptr() - cache_k.data_ptr())
+        assert off % row == 0
+        return off // row, view.shape[1]
+
+    def fake_monarch(q, k_cache, v_cache, new_k, new_v, start_idx, end_idx, *a, **kw):
+        k_cache[:, start_idx:end_idx] = new_k
+        v_cache[:, start_idx:end_idx] = new_v
+        rec.update(branch=0, view=view_of(rec["cache_k"], k_cache), slot=(int(start_idx), int(end_idx)))
+        return torch.zeros_like(q)
+
+    def fake_attention(q, k, v, *a, **kw):
+        rec.update(branch=1, view=view_of(rec["cache_k"], k), slot=None)
+        return torch.zeros_like(q)
+
+    cm.monarch_attn_with_kv_cache = fake_monarch
+    cm.attention = fake_attention
+    stride = cases.BOOKKEEPING_ID_STRIDE
+    for name, sc in cases.BOOKKEEPING_SCENARIOS.items():
+        for k in ("MONARCH_ATTN_FRAMEWISE", "USE_DENSE_INIT"):
+            os.environ.pop(k, None)
+        os.environ["MONARCH_ATTN_FRAMEWISE"] = "1"
+        if sc.get("dense_init"):
+            os.environ["USE_DENSE_INIT"] = "1"
+        torch.manual_seed(7)
+        mod = cm.CausalWanSelfAttention(256, 2, local_attn_size=sc["local_attn_size"], sink_size=sc["sink_size"])
+        n_cache = sc["cache_frames"] * frame
+        kv = {"k": torch.zeros(1, n_cache, 2, 128), "v": torch.zeros(1, n_cache, 2, 128),
+              "global_end_index": torch.tensor([0], dtype=torch.long),
+              "local_end_index": torch.tensor([0], dtype=torch.long)}
+        kv["k"][0, :, 0, 0] = -(torch.arange(n_cache, dtype=torch.float32) + 1)      # "never written" ids
+        grid = torch.tensor([[3, 30, 52]], dtype=torch.long)
+        freqs = torch.polar(torch.ones(1024, 64, dtype=torch.float64), torch.zeros(1024, 64, dtype=torch.float64))
+        rows = []
+        ids_rows = []
+        with torch.no_grad():
+            for chunk, repeats in sc["calls"]:
+                for _ in range(repeats):
+                    current_start = chunk * 3 * frame
+                    x = torch.randn(1, 3 * frame, 256)
+                    before = (int(kv["global_end_index"]), int(kv["local_end_index"]))
+                    rec.clear()
+                    rec["cache_k"] = kv["k"]
+                    mod(x, torch.tensor([3 * frame]), grid, freqs, None, kv_cache=kv, current_start=current_start)
+                    col = kv["k"][0, :, 0, 0]
+                    fresh = (col != col.round()).nonzero().flatten()      # rows holding projected keys = the slot
+                    assert fresh.numel() == 3 * frame and int(fresh[-1] - fresh[0]) == 3 * frame - 1
+                    col[fresh] = current_start + torch.arange(3 * frame, dtype=torch.float32) + 1
+                    v0, vlen = rec["view"]
+                    s0 = int(fresh[0]) - v0
+                    if rec["slot"] is not None:
+                        assert rec["slot"] == (s0, s0 + 3 * frame)
+                    rows.append([current_start, before[0], before[1], rec["branch"], v0, vlen, s0, s0 + 3 * frame,
+                                 int(kv["global_end_index"]), int(kv["local_end_index"])])
+                    ids_rows.append(col[::stride].to(torch.int64).numpy().copy())
+        out[f"book_{name}_calls"] = np.array(rows, dtype=np.int64)
+        out[f"book_{name}_ids"] = np.stack(ids_rows).astype(np.int32)
+
+
+def make_pins():
+    ns, _, _ = load_reference()
+    out = {}
+    gradient_pins(ns, out)
+    dense_pins(out)
+    bookkeeping_pins(out)
+    np.savez_compressed(HERE / "pins_golden.npz", **out)
+    sz = (HERE / "pins_golden.npz").stat().st_size
+    print(f"pins: wrote {len(out)} arrays, {sz/1e6:.2f} MB")
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    torch.set_num_threads(os.cpu_count() or 1)
+    if "--only-pins" not in sys.argv:
+        main()
+    make_pins()

@@ -157,9 +157,82 @@ def test_autograd_function(sfb, only_new):
     if only_new:
         assert kv.grad is None and vv.grad is None
     else:
-        grad_close(kv.grad, ref["kc"], 1e-2, "k_cache.grad")
-        grad_close(vv.grad, ref["vc"], 1e-2, "v_cache.grad")
-        assert not kv.grad[:, c["start"]:c["end"]].any()
+        # the reference's convention: gradient of the cache content after the write, the written slot holding
+        # the new keys' / values' gradient in Monarch order
+        ft, hr, wr, h, w = c["blocking"]
+        s, e = c["start"], c["end"]
+        full_k, full_v = ref["kc"].clone(), ref["vc"].clone()
+        full_k[:, s:e] = orc.to_monarch_order(ref["nk"], ft, hr, wr, h, w).reshape(full_k[:, s:e].shape)
+        full_v[:, s:e] = orc.to_monarch_order(ref["nv"], ft, hr, wr, h, w).reshape(full_v[:, s:e].shape)
+        grad_close(kv.grad, full_k, 1e-2, "k_cache.grad")
+        grad_close(vv.grad, full_v, 1e-2, "v_cache.grad")
+
+
+@pytest.fixture(scope="module")
+def pins():
+    from conftest import ROOT
+    return np.load(ROOT / "tests" / "golden" / "pins_golden.npz")
+
+
+CS = cases.PIN_CHANNEL_STRIDE
+
+
+@pytest.mark.parametrize("ci", range(len(cases.SMALL_BLOCKINGS)))
+@pytest.mark.parametrize("only_new", [False, True])
+def test_gradients_match_reference_fixtures(sfb, pins, ci, only_new):
+    """The autograd path against gradients produced by the reference's own gradient oracle (autograd through
+    its monarch_attn_with_kv_cache_ref, both grad_only_new_kv modes, as its run_kv_cache_test does)."""
+    c = cases.grad_case(ci)
+    dev = "cuda"
+    q = bf(c["q"]).to(dev).requires_grad_()
+    nk, nv = bf(c["nk"]).to(dev).requires_grad_(), bf(c["nv"]).to(dev).requires_grad_()
+    kv = bf(c["kbuf"]).to(dev)[:, :c["n_kv"]].clone().requires_grad_(not only_new)
+    vv = bf(c["vbuf"]).to(dev)[:, :c["n_kv"]].clone().requires_grad_(not only_new)
+    z = sfb.monarch_attn_with_kv_cache(q, kv, vv, nk, nv, c["start"], c["end"], *c["blocking"], sm_scale=c["sm_scale"],
+                                       grad_only_new_kv=only_new)
+    z.backward(bf(c["g"]).to(dev))
+    torch.cuda.synchronize()
+    key = f"grad_{c['name']}_"
+    ref = lambda n: torch.from_numpy(pins[key + n])
+    err = (z.detach().float().cpu()[..., ::CS] - ref("z")).abs().max().item()
+    assert err <= 2e-2, f"forward max-abs {err:.3e}"
+    grad_close(q.grad[..., ::CS], ref("dq"), 1e-2, "q.grad")
+    grad_close(nk.grad[..., ::CS], ref("dnk"), 1e-2, "new_k.grad")
+    grad_close(nv.grad[..., ::CS], ref("dnv"), 1e-2, "new_v.grad")
+    if only_new:
+        assert kv.grad is None and vv.grad is None
+    else:
+        grad_close(kv.grad[..., ::CS], ref("dkc"), 1e-2, "k_cache.grad")
+        grad_close(vv.grad[..., ::CS], ref("dvc"), 1e-2, "v_cache.grad")
+
+
+@pytest.mark.parametrize("i", range(len(cases.CAUSAL_GRAD_CASES)))
+def test_block_causal_gradients_match_reference_fixtures(sfb, pins, i):
+    """monarch_attn with block_causal_size under autograd against autograd through the reference's
+    monarch_attn_causal_ref."""
+    c = cases.causal_grad_case(i)
+    q, k, v = (bf(c[n]).cuda().requires_grad_() for n in ("q", "k", "v"))
+    z = sfb.monarch_attn(q, k, v, *c["blocking"], sm_scale=c["sm_scale"], block_causal_size=c["block_causal"])
+    z.backward(bf(c["g"]).cuda())
+    torch.cuda.synchronize()
+    key = f"causalgrad_{c['name']}_"
+    for name, t in (("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+        grad_close(t[..., ::CS], torch.from_numpy(pins[key + name]), 1e-2, name)
+
+
+def test_cache_rewrite_before_backward_is_an_error(sfb):
+    """The saved cache is what the backward kernels read; overwriting it before backward must fail loudly (as
+    the reference's in-place slice assignment does through autograd's version counters)."""
+    c = cases.grad_case(0)
+    dev = "cuda"
+    q = bf(c["q"]).to(dev).requires_grad_()
+    nk, nv = bf(c["nk"]).to(dev), bf(c["nv"]).to(dev)
+    kv, vv = bf(c["kbuf"]).to(dev)[:, :c["n_kv"]].clone(), bf(c["vbuf"]).to(dev)[:, :c["n_kv"]].clone()
+    z = sfb.monarch_attn_with_kv_cache(q, kv, vv, nk, nv, c["start"], c["end"], *c["blocking"])
+    with torch.no_grad():
+        sfb.monarch_attn_with_kv_cache(q.detach(), kv, vv, nk, nv, c["start"], c["end"], *c["blocking"])
+    with pytest.raises(RuntimeError, match="modified by an inplace operation"):
+        z.sum().backward()
 
 
 @pytest.mark.parametrize("ci,causal_frames", [(0, None), (0, 2), (2, 1), (1, None), (3, 3)])

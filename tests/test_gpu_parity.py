@@ -183,9 +183,12 @@ def test_monarch_baseline_config1_vs_golden(sfb, golden):
 
 
 @pytest.mark.parametrize("name,ft,hr,wr,k_chunks", [("framewise", 1, 1, 1, 7), ("tied3frame", 3, 1, 1, 4),
-                                                      ("reduce2xh", 1, 2, 1, 3), ("reduce4xw2xh", 1, 2, 4, 2)])
+                                                      ("reduce2xh", 1, 2, 1, 3), ("reduce4xw2xh", 1, 2, 4, 2),
+                                                      ("tied3frame", 3, 1, 1, 7), ("reduce2xh", 1, 2, 1, 7),
+                                                      ("reduce4xw2xh", 1, 2, 4, 7), ("framewise", 1, 1, 1, 1)])
 def test_monarch_rollout_shapes_vs_oracle(sfb, name, ft, hr, wr, k_chunks):
-    """Wan-1.3B chunk (4680 queries) against k cached chunks; 2 of the heads are checked on the CPU."""
+    """Wan-1.3B chunk (4680 queries) against k cached chunks, every blocking at the full cache length (k = 7,
+    where the unit lists, the F splits and the bridge are largest); 2 of the heads are checked on the CPU."""
     rng = np.random.default_rng(900 + k_chunks)
     B, H, D, h, w = 1, 4, 128, 30, 52
     n = 3 * h * w
@@ -285,6 +288,17 @@ def test_dense_attention(sfb, n_q, n_kv):
     got = sfb.attention(q.cuda(), kd[:, :n_kv], vd[:, :n_kv])      # strided views, as the model passes them
     ref = orc.dense_attention(q.float(), k[:, :n_kv].float(), v[:, :n_kv].float())
     check_close(got, ref, f"dense {n_q}x{n_kv}")
+
+
+@pytest.mark.parametrize("i", range(len(cases.DENSE_CASES)))
+def test_dense_attention_vs_reference_fixture(sfb, i):
+    """Against the reference's own attention() run through its SDPA branch in fp32 (pins_golden.npz)."""
+    from conftest import ROOT
+    pins = np.load(ROOT / "tests" / "golden" / "pins_golden.npz")
+    c = cases.dense_case(i)
+    kd, vd = bf(c["kbuf"]).cuda(), bf(c["vbuf"]).cuda()
+    got = sfb.attention(bf(c["q"]).cuda(), kd[:, :c["n_kv"]], vd[:, :c["n_kv"]])
+    check_close(got, torch.from_numpy(pins[f"dense_{i}_fp32"]), f"dense case {i}")
 
 
 def test_dense_with_cache_write(sfb):
