@@ -360,6 +360,73 @@ def run_model(args, rank, world, device, barrier):
                           "gpu_launches": int(launches), "clocks": clocks}), flush=True)
 
 
+def run_probe_dsmem(device):
+    """Store bandwidth between the CTAs of a cluster through distributed shared memory (sfm_probe_dsmem_store):
+    the ceiling of an on-chip hand-off between the row step and the column step."""
+    import ctypes as C
+    from self_forcing_b200 import _lib
+    lib = _lib.load()
+    rows = []
+    for cluster in (1, 2, 4, 8, 16):
+        for remote in ((0,) if cluster == 1 else (0, 1)):
+            for pattern in (0, 1):
+                ms, ctas, nbytes = C.c_float(), C.c_int(), C.c_double()
+                rc = lib.sfm_probe_dsmem_store(cluster, pattern, remote, 2000, C.byref(ms), C.byref(ctas), C.byref(nbytes))
+                row = {"cluster": cluster, "remote": bool(remote), "pattern": "row-per-lane 32 B" if pattern == 0 else "coalesced 16 B"}
+                if rc:
+                    row["error"] = lib.sfm_error_string(rc).decode()
+                else:
+                    row.update(ctas=ctas.value, ms=ms.value, tb_per_s=nbytes.value / ms.value * 1e-9,
+                               bytes_per_clk_per_sm=nbytes.value / (ms.value * 1e-3) / ctas.value / 1.965e9)
+                rows.append(row)
+    print(json.dumps({"probe": "dsmem_store", "sm_clock_assumed_mhz": 1965, "rows": rows}, indent=1))
+
+
+def run_incumbent(args, device):
+    """The reference's own Triton Monarch path (monarch_attn_with_kv_cache, num_iters=1: _al_cl_y_fwd + _z_fwd
+    in 3x3 group chunks, monarch_attn.py:1227-1323), imported unmodified from the staged checkout and timed on
+    this GPU beside this package's op on the same tensors (op only: both write the new keys and attend;
+    RoPE is outside).  The first call autotunes (minutes); the timed calls come after it."""
+    import importlib.util
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_harness as rh
+    root = rh.reference_root()
+    if root is None:
+        print(json.dumps({"incumbent": "unavailable", "why": "reference sources not staged (baseline/stage_reference.py)"}))
+        return
+    spec = importlib.util.spec_from_file_location("ref_monarch_attn", root / "wan/modules/monarch_attn.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    import self_forcing_b200 as sfb
+    ft, hr, wr = BLOCKINGS[args.blocking]
+    out = {"blocking": args.blocking, "triton": __import__("triton").__version__, "rows": []}
+    for k in ([args.k] if args.k_only else [7, 4, 1]):
+        g = torch.Generator(device="cpu").manual_seed(k)
+        mk = lambda m: torch.randn(1, m, HEADS, HEAD_DIM, generator=g).to(torch.bfloat16).to(device)
+        n_kv = k * CHUNK
+        q, nk, nv, kc, vc = mk(CHUNK), mk(CHUNK), mk(CHUNK), mk(n_kv), mk(n_kv)
+        kc2, vc2 = kc.clone(), vc.clone()
+        ref_call = lambda: ref.monarch_attn_with_kv_cache(q, kc, vc, nk, nv, n_kv - CHUNK, n_kv, ft, hr, wr, H_GRID, W_GRID, num_iters=1)
+        our_call = lambda: sfb.monarch_attn_with_kv_cache(q, kc2, vc2, nk, nv, n_kv - CHUNK, n_kv, ft, hr, wr, H_GRID, W_GRID)
+        row = {"k": k}
+        with torch.no_grad():
+            t0 = time.perf_counter()
+            try:
+                zr = ref_call()
+                torch.cuda.synchronize()
+            except Exception as exc:                                   # Triton may not compile here: record why
+                row["error"] = repr(exc)[:400]
+                out["rows"].append(row)
+                continue
+            row["first_call_s"] = time.perf_counter() - t0
+            zo = our_call()
+            row["max_abs_diff"] = (zr.float() - zo.float()).abs().max().item()
+            row["reference_triton_ms"] = time_steps(ref_call, args.steps, args.warmup, lambda: None) / args.steps
+            row["ours_ms"] = time_steps(our_call, args.steps, args.warmup, lambda: None) / args.steps
+        out["rows"].append(row)
+    print(json.dumps(out, indent=1))
+
+
 def run_backward(args, sfb, rank, world, device, barrier):
     """Forward + backward of the Monarch attention op at the headline shape (one 3-frame chunk against k cached
     chunks, 12 heads): the call a training rollout makes per layer (gradients of q and of the chunk's own keys
@@ -508,6 +575,12 @@ def main():
     ap.add_argument("--dense-init", action="store_true", help="with --rollout: dense attention for the first chunk")
     ap.add_argument("--p2p", action="store_true",
                     help="with --ulysses: the kernels gather / scatter over peer memory instead of the two NCCL all-to-alls")
+    ap.add_argument("--probe-dsmem", action="store_true",
+                    help="measure store bandwidth between the CTAs of a cluster (distributed shared memory) and exit")
+    ap.add_argument("--incumbent", action="store_true",
+                    help="time the reference's own Triton Monarch op beside this package's on the same tensors "
+                         "(needs the staged reference sources) and exit")
+    ap.add_argument("--k-only", action="store_true", help="with --incumbent: only the cache length given by --k")
     ap.add_argument("--model", default=None, choices=["1.3b", "14b"],
                     help="time the whole causal DiT rollout through the reference's unmodified model and pipeline code "
                          "(needs the staged reference sources, see baseline/stage_reference.py) instead of the headline workload")
@@ -538,6 +611,13 @@ def main():
         barrier = lambda: dist.barrier()
     else:
         barrier = lambda: None
+
+    if args.probe_dsmem or args.incumbent:
+        if rank == 0:
+            run_probe_dsmem(device) if args.probe_dsmem else run_incumbent(args, device)
+        if use_dist:
+            dist.destroy_process_group()
+        return
 
     if args.model:
         run_model(args, rank, world, device, barrier)

@@ -167,6 +167,17 @@ size_t sfm_static_scratch_bytes(void);
 int sfm_workspace_status(const void* workspace, void* stream);
 
 /*
+ * The same report for the two paths that have no caller workspace.  sfm_static_scratch_status: the last
+ * sfm_monarch_fwd_static call on the current device (its status word is the first word of the built-in
+ * array).  sfm_dense_status: the dense-attention kernels on the current device; their word is shared by
+ * all streams and keeps the first failure since the previous sfm_dense_status call, which clears it.
+ * Both synchronise `stream`.
+ * Replaces: nothing in the reference.
+ */
+int sfm_static_scratch_status(void* stream);
+int sfm_dense_status(void* stream);
+
+/*
  * Block-causal Monarch attention without a cache: q, k, v [B, N, H, D] natural order,
  * contiguous.  Query groups of causal block c attend the key groups of blocks 0..c;
  * causal_groups = groups per causal block (0 = no mask).  k_mon / v_mon are scratch
@@ -301,6 +312,16 @@ int sfm_monarch_bwd(const void* q, int64_t q_batch_stride,
 long long sfm_launch_count(void);
 int sfm_profile_enable(int on);
 int sfm_profile_read(float* ms, long long* launches, int n_classes);
+
+/*
+ * Diagnostic (no counterpart in the reference): store bandwidth between the CTAs of a thread-block
+ * cluster through distributed shared memory, the traffic pattern of an on-chip hand-off between the row
+ * step and the column step.  `cluster` CTAs per cluster (1, 2, 4, 8, 16), one CTA per SM, `iters` passes of
+ * 64 KB per CTA; pattern 0 = one 256-byte row per lane written in 32-byte pieces, 1 = coalesced 16-byte
+ * stores; remote 0 = own shared memory, 1 = the peers'.  Plain stores to cluster-mapped addresses only.
+ * Returns elapsed milliseconds, CTAs launched and bytes stored.
+ */
+int sfm_probe_dsmem_store(int cluster, int pattern, int remote, int iters, float* ms, int* ctas, double* bytes);
 
 #ifdef __cplusplus
 }

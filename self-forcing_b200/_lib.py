@@ -41,9 +41,12 @@ SIGNATURES = {
     "sfm_monarch_bwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_void_p] * 5 +
                         [C.c_size_t] + [C.c_int] * 10 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "sfm_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sfm_static_scratch_status": (C.c_int, [C.c_void_p]),
+    "sfm_dense_status": (C.c_int, [C.c_void_p]),
     "sfm_launch_count": (C.c_longlong, []),
     "sfm_profile_enable": (C.c_int, [C.c_int]),
     "sfm_profile_read": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "sfm_probe_dsmem_store": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

@@ -349,6 +349,17 @@ extern "C" int sfm_monarch_fwd_static(const void* q, int64_t q_batch_stride, con
                        budget, (cudaStream_t)stream);
 }
 
+// Status word of the last sfm_monarch_fwd_static call on the current device (first word of the built-in
+// array): waits for `stream` and reports SFM_OK or SFM_ERR_DEVICE_STATUS, like sfm_workspace_status.
+extern "C" int sfm_static_scratch_status(void* stream) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return SFM_ERR_UNSUPPORTED;
+    if (!g_static_scratch_ptr[dev]) return SFM_OK;                 // never used on this device
+    return sfm_workspace_status(g_static_scratch_ptr[dev], stream);
+}
+
 extern "C" int sfm_monarch_nocache_fwd(const void* q, const void* k, const void* v, void* k_mon, void* v_mon,
                                        void* out, void* workspace, size_t workspace_bytes, int B, int H, int D, int N,
                                        int f_tied, int h_reduce, int w_reduce, int h, int w, float sm_scale,

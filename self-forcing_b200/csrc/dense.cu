@@ -12,7 +12,9 @@ namespace sfm {
 int launch_dense_tc(const CUtensorMap* maps, __nv_bfloat16* out, int B, int H, int n_q, int n_kv, float scale, int* status,
                     int num_sms, cudaStream_t s);
 namespace {
-// Set by the kernel when one of its bounded waits gives up (diagnostic; 0 = ok).
+// Set (once, by compare-and-swap from 0) by the kernel when one of its bounded waits gives up; 0 = ok.
+// One word per device, shared by every stream, never cleared by a launch: it keeps the first failure since
+// the last sfm_dense_status call, which reads and clears it.
 __device__ int g_dense_status;
 }  // namespace
 }  // namespace sfm
@@ -49,4 +51,17 @@ extern "C" int sfm_dense_fwd(const void* q, int64_t q_batch_stride, const void* 
     if ((rc = make_tmap_bf16(&maps[1], v, 4, dk, sk, box))) return rc;
     if ((rc = make_tmap_bf16(&maps[2], q, 4, dq, sq, box))) return rc;
     return launch_dense_tc(maps, (__nv_bfloat16*)out, B, H, n_q, n_kv, sm_scale, status, num_sms, (cudaStream_t)stream);
+}
+
+// Waits for `stream`, then reports (and clears) the status word of the dense-attention kernels on the
+// current device: SFM_OK, or SFM_ERR_DEVICE_STATUS if a launch since the last call gave up on a bounded wait.
+extern "C" int sfm_dense_status(void* stream) {
+    int* status = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_dense_status);
+    int st = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&st, status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e == cudaSuccess && st != 0) e = cudaMemsetAsync(status, 0, sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    return st == 0 ? SFM_OK : SFM_ERR_DEVICE_STATUS;
 }

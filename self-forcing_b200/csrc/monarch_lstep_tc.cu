@@ -33,14 +33,8 @@ using namespace tc;
 
 namespace {
 
-#ifndef SFM_L_ASTAGES
-#define SFM_L_ASTAGES 2
-#endif
-#ifndef SFM_L_YSTAGES
-#define SFM_L_YSTAGES 3
-#endif
-constexpr int kAStages = SFM_L_ASTAGES;    // key (aL) tile ring, released as soon as the S GEMM has read a tile
-constexpr int kYStages = SFM_L_YSTAGES;    // value (Y) tile ring, released after the PV GEMM
+constexpr int kAStages = 2;    // key (aL) tile ring, released as soon as the S GEMM has read a tile
+constexpr int kYStages = 3;    // value (Y) tile ring, released after the PV GEMM
 constexpr int kThreads = 512;
 constexpr int kKT = 128;                   // keys per tile
 constexpr int kMaxU = 8;                   // units per group (the bias ring is sized for it)
@@ -59,16 +53,8 @@ struct LTcParams {
     int n_kv;        // dense: keys per (batch, head)
     int q_tiles;     // dense: ceil(n_q / 128)
     int* status;
-#ifdef SFM_TRACE
-    long long* trace;   // debug build only: per-role, per-tile cycle stamps of CTA 0
-#endif
 };
 
-#ifdef SFM_TRACE
-#define LTRACE(role, it, ev) do { if (blockIdx.x == 0 && (it) < 32) trace_s[((role) * 32 + (it)) * 4 + (ev)] = clock64(); } while (0)
-#else
-#define LTRACE(role, it, ev) do {} while (0)
-#endif
 
 struct __align__(16) Barriers {
     alignas(16) float cl[4][kMaxU][kKT];   // bias slices, per unit slot: two ring slots for each softmax warpgroup
@@ -130,11 +116,6 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     unsigned char* y_s = a_s + kAStages * kTileBytes;
     Barriers* bars = reinterpret_cast<Barriers*>(y_s + kYStages * kTileBytes);
 
-#ifdef SFM_TRACE
-    __shared__ long long trace_s[8 * 32 * 4];
-    for (int i = threadIdx.x; i < 8 * 32 * 4; i += blockDim.x) trace_s[i] = 0;
-    __syncthreads();
-#endif
     const MonarchParams& p = lp.mp;
     const Blocking& blk = p.blk;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -269,7 +250,6 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 const int w = t & 1;
                 const int idx = cnt[w]++;
                 const int gt = cnt[0] + cnt[1] - 1;
-                if (lane == 0) LTRACE(4, gt, 0);
                 if (!kDense) {
                     // ring slot: two per softmax warpgroup, released by its threads after their last read
                     const int cslot = w + 2 * (idx & 1);
@@ -309,7 +289,6 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                             tma_load_3d(at, &tal, &bars->a_full[sa], 0, t * kKT, aj);
                             tma_load_3d(at + kKT * 128, &tal, &bars->a_full[sa], 64, t * kKT, aj);
                         }
-                        LTRACE(4, gt, 1 + (us > 0) + (us > 2));
                     }
                 }
             }
@@ -326,9 +305,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 for (int t = 0; ok && t < n_tiles; ++t)
                     for (int us = 0; us < nu; ++us, ++gy) {
                         const int sy = gy % kYStages;
-                        if (us == 0) LTRACE(5, gy / 4, 0);
                         if (gy >= kYStages && !mbar_wait(&bars->y_empty[sy], ((gy / kYStages) - 1) & 1)) { fail(12); ok = false; break; }
-                        LTRACE(5, gy / 4, 1 + (us > 0) + (us > 2));
                         unsigned char* yt = y_s + sy * kTileBytes;
                         mbar_arrive_expect_tx(&bars->y_full[sy], (uint32_t)kTileBytes);
                         if (kDense) {
@@ -360,9 +337,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     const int w = t & 1;
                     const int idx = cnt[w]++;
                     const int gt = cnt[0] + cnt[1] - 1;
-                    LTRACE(0, gt, 0);
                     if (idx >= 1 && !mbar_wait(&bars->sp_free[w], (idx - 1) & 1)) { fail(25); ok = false; break; }
-                    LTRACE(0, gt, 1);
                     for (int us = 0; us < nu; ++us, ++ga) {
                         const int sa = ga % kAStages;
                         if (!mbar_wait(&bars->a_full[sa], (ga / kAStages) & 1)) { fail(21); ok = false; break; }
@@ -376,9 +351,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                             else mma_ss_masked(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0, dis);
                         }
                         mma_commit(&bars->a_empty[sa]);
-                        if (us == 0) LTRACE(0, gt, 2);
                     }
-                    LTRACE(0, gt, 3);
                     if (!ok) break;
                     mma_commit(&bars->s_full[w]);
                     if (t + 1 == n_tiles) mma_commit(&bars->q_empty);
@@ -399,9 +372,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     const int w = t & 1;
                     const int idx = cnt[w]++;
                     const int gt = cnt[0] + cnt[1] - 1;
-                    LTRACE(1, gt, 0);
                     if (!mbar_wait(&bars->p_full[w], idx & 1)) { fail(22); ok = false; break; }
-                    LTRACE(1, gt, 1);
                     // first GEMM of the group into this accumulator overwrites it: the previous group's
                     // result must have been read
                     if (t < 2 && gc > 0 && !mbar_wait(&bars->o_free, (gc - 1) & 1)) { fail(23); ok = false; break; }
@@ -420,9 +391,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                                               (t >= 2) || (kk > 0), dis);
                         }
                         mma_commit(&bars->y_empty[sy]);
-                        if (us == 0) LTRACE(1, gt, 2);
                     }
-                    LTRACE(1, gt, 3);
                     if (!ok) break;
                     mma_commit(&bars->pv_done[w]);
                     mma_commit(&bars->sp_free[w]);
@@ -448,9 +417,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             int my_tiles = 0;
             for (int t = w; t < n_tiles; t += 2) {
                 const int valid = min(kKT, n_keys - t * kKT);                 // keys of this tile that exist
-                if (row == 0) LTRACE(2 + w, idx, 0);
                 if (!mbar_wait(&bars->s_full[w], idx & 1)) { fail(31); ok = false; break; }
-                if (row == 0) LTRACE(2 + w, idx, 1);
                 const int cslot = w + 2 * (idx & 1);
                 const float* cs = bars->cl[cslot][us];
                 if (!kDense && !mbar_wait(&bars->cl_full[cslot], (idx >> 1) & 1)) { fail(33); ok = false; break; }
@@ -509,7 +476,6 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     }
                     tmem_wait_st();
                 }
-                if (row == 0) LTRACE(2 + w, idx, 2);
                 const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
                 // pass 2: P = exp2(logit - m), packed bf16 written back over the S columns already consumed
                 const uint64_t negm2 = f2_pack(neg_m, neg_m);
@@ -552,7 +518,6 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 }
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[w]);
-                if (row == 0) LTRACE(2 + w, idx - 1, 3);
             }
         }
     } else if (warp >= 12) {
@@ -623,18 +588,10 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
-#ifdef SFM_TRACE
-    if (lp.trace && blockIdx.x == 0)
-        for (int i = threadIdx.x; i < 8 * 32 * 4; i += blockDim.x) lp.trace[i] = trace_s[i];
-#endif
 }
 
 }  // namespace
 
-#ifdef SFM_TRACE
-long long* g_sfm_trace_l = nullptr;
-extern "C" void sfm_debug_set_trace_l(long long* p) { g_sfm_trace_l = p; }
-#endif
 
 // Launches the tensor-core column step for one chunk as a persistent grid.  maps = {aL, Y} with a
 // (64, 128 keys, 1) box and the 5-D query-row map (box rows = ceil(b1/4)).
@@ -655,9 +612,6 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
     lp.q_rows_tma = (p.blk.f_tied == 1 || p.blk.h_reduce == 1) ? 1 : 0;
     lp.n_kv = 0;
     lp.q_tiles = 0;
-#ifdef SFM_TRACE
-    lp.trace = g_sfm_trace_l;
-#endif
     const int n_groups = (lp.n_units + lp.U - 1) / lp.U;
     dim3 grid(n_groups < num_sms ? n_groups : num_sms);
     auto kernel = p.causal_groups > 0 ? monarch_l_tc_kernel<false, true> : monarch_l_tc_kernel<false, false>;
@@ -686,9 +640,6 @@ int launch_dense_tc(const CUtensorMap* maps, __nv_bfloat16* out, int B, int H, i
     lp.n_kv = n_kv;
     lp.q_rows_tma = 1;
     lp.status = status;
-#ifdef SFM_TRACE
-    lp.trace = nullptr;
-#endif
     dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
     cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;

@@ -49,22 +49,8 @@ struct RTcParams {
     int tiles;             // tiles per (batch*head) of the chunk
     int n_units;           // nbh * tiles * b1 * fsplit
     int* status;           // device status word (0 = ok)
-#ifdef SFM_TRACE
-    long long* trace;      // debug build only: per-role, per-step cycle stamps of CTA 0
-    int ablate;            // debug build only: bit 0 skips the softmax arithmetic, bit 1 the stores, bit 2 the drains
-#endif
 };
 
-#ifdef SFM_TRACE
-#define TRACE(role, it, ev) do { if ((it) < 32) trace_s[((role) * 32 + (it)) * 4 + (ev)] = clock64(); } while (0)
-#else
-#define TRACE(role, it, ev) do {} while (0)
-#endif
-#ifdef SFM_TRACE
-#define ABLATE(bit) (rp.ablate & (bit))
-#else
-#define ABLATE(bit) 0
-#endif
 
 struct RUnit {
     int bhl, tile, k, f_begin, n_it;
@@ -123,11 +109,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     unsigned char* kv_s = q_s + kQBytes;
     Barriers* bars = reinterpret_cast<Barriers*>(kv_s + (N_S > 64 ? 2 * 2 * kStageBytes : kStages * kStageBytes));
 
-#ifdef SFM_TRACE
-    __shared__ long long trace_s[8 * 32 * 4];
-    for (int i = threadIdx.x; i < 8 * 32 * 4; i += blockDim.x) trace_s[i] = 0;
-    __syncthreads();
-#endif
     const MonarchParams& p = rp.mp;
     const Blocking& blk = p.blk;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -184,11 +165,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStg;
-                    if (ABLATE(8)) continue;
                     if (g >= kStg && !mbar_wait(&bars->kv_empty[s], ((g / kStg) - 1) & 1)) { fail(11); break; }
                     const int tok = ((un.f_begin + i) * b1 + un.k) * b2;
                     unsigned char* st = kv_s + s * kStgBytes;
-                    TRACE(0, g, 0);
                     mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(4 * kHalf));
                     tma_load_4d(st, &tk, &bars->kv_full[s], 0, hd, tok, b);
                     tma_load_4d(st + kHalf, &tk, &bars->kv_full[s], 64, hd, tok, b);
@@ -214,7 +193,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStg;
-                    if (!ABLATE(8) && !mbar_wait(&bars->kv_full[s], (g / kStg) & 1)) { fail(21); ok = false; break; }
+                    if (!mbar_wait(&bars->kv_full[s], (g / kStg) & 1)) { fail(21); ok = false; break; }
                     if (g >= 2 && !mbar_wait(&bars->sp_free[g & 1], ((g >> 1) - 1) & 1)) { fail(25); ok = false; break; }
                     tc_fence_after();
                     const uint64_t kd = k_desc0 + (uint64_t)((s * kStgBytes) >> 4);
@@ -242,11 +221,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
                 const RUnit un = decode_unit<kCausal>(rp, u);
                 for (int i = 0; i < un.n_it; ++i, ++g) {
-                    TRACE(1, g, 0);
                     if (!mbar_wait(&bars->p_full[g & 1], (g >> 1) & 1)) { fail(22); ok = false; break; }
-                    TRACE(1, g, 1);
                     if (g > 0 && !mbar_wait(&bars->o_free, (g - 1) & 1)) { fail(23); ok = false; break; }
-                    TRACE(1, g, 2);
                     tc_fence_after();
                     const int s = g % kStg;
                     const uint64_t bd = kv_desc_mn0 + (uint64_t)((s * kStgBytes) >> 4);
@@ -257,7 +233,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     mma_commit(&bars->o_full);
                     mma_commit(&bars->kv_empty[s]);
                     mma_commit(&bars->sp_free[g & 1]);
-                    TRACE(1, g, 3);
                 }
             }
         }
@@ -282,11 +257,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             const int f_allowed = kCausal ? ((p.a0 + g_first + gl) / p.causal_groups + 1) * p.causal_groups : p.F;
             for (int i = 0; i < un.n_it; ++i, ++g) {
                 if ((g & 1) != wg) continue;
-                if (lane == 0 && quad == 0) TRACE(2, g, 0);
                 if (!mbar_wait(&bars->s_full[wg], (g >> 1) & 1)) { fail(31); ok = false; break; }
                 tc_fence_after();
-                if (lane == 0 && quad == 0) TRACE(2, g, 1);
-                if (warp_active && !ABLATE(1)) {
+                if (warp_active) {
                     if constexpr (!kWide) {
                     uint32_t raw[N_S];
                     if constexpr (N_S == 64) {
@@ -301,7 +274,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                         tmem_ld16(s_t, *reinterpret_cast<uint32_t(*)[16]>(&raw[0]));
                     }
                     tmem_wait_ld();
-                    if (lane == 0 && quad == 0) TRACE(6, g, 0);
                     // only the last 16 columns can lie beyond b2
 #pragma unroll
                     for (int c = N_S - 16; c < N_S; ++c)
@@ -329,7 +301,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     z += zh;
                     ent += enth;
                     const float inv_z = 1.0f / z;
-                    if (lane == 0 && quad == 0) TRACE(6, g, 1);
                     const uint64_t invz2 = f2_pack(inv_z, inv_z);
                     uint32_t pk[N_S / 2];
 #pragma unroll
@@ -355,7 +326,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                         tmem_st16(s_t, p2);   // 8 packed columns are the operand; the other 8 lie inside the S buffer
                     }
                     tmem_wait_st();
-                    if (lane == 0 && quad == 0) TRACE(6, g, 2);
                     if (row_ok) {
                         const int key = (un.f_begin + i) * b1 + un.k;
                         p.cL[aj * p.n_keys_c + key] =
@@ -430,7 +400,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 }
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[wg]);
-                if (lane == 0 && quad == 0) TRACE(2, g, 2);
             }
         }
     } else if (warp >= 11) {
@@ -447,10 +416,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             const int ng = min(rp.groups_per_tile, p.na - g_first);
             const bool warp_active = quad * 32 < ng * RG;
             for (int i = 0; ok && i < un.n_it; ++i, ++g) {
-                if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 0);
                 if (!mbar_wait(&bars->o_full, g & 1)) { fail(41); ok = false; break; }
                 tc_fence_after();
-                if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 1);
                 // This thread's bridge row: 256 bytes at (aj, key), written as 32-byte vectors.
                 const int gl = row / RG, j = row - gl * RG;
                 const bool row_ok = warp_active && gl < ng && j < b2;
@@ -460,7 +427,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {                 // 64 columns at a time
                     uint32_t ra[32], rb[32];
-                    if (warp_active && !ABLATE(4)) {
+                    if (warp_active) {
                         tmem_ld32(o_t + h * 64, ra);
                         tmem_ld32(o_t + h * 64 + 32, rb);
                         tmem_wait_ld();
@@ -468,9 +435,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     if (h == 1) {
                         tc_fence_before();
                         mbar_arrive(&bars->o_free);            // accumulator may be overwritten from here on
-                        if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 2);
                     }
-                    if (row_ok && !ABLATE(2)) {
+                    if (row_ok) {
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
                             const uint32_t (&r)[32] = c ? rb : ra;
@@ -485,7 +451,6 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                         }
                     }
                 }
-                if (which == 0 && quad == 0 && lane == 0) TRACE(3, g, 3);
             }
         }
     }
@@ -493,20 +458,10 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
-#ifdef SFM_TRACE
-    if (rp.trace && blockIdx.x == 0)
-        for (int i = threadIdx.x; i < 8 * 32 * 4; i += blockDim.x) rp.trace[i] = trace_s[i];
-#endif
 }
 
 }  // namespace
 
-#ifdef SFM_TRACE
-long long* g_sfm_trace = nullptr;
-int g_sfm_ablate = 0;
-extern "C" void sfm_debug_set_trace(long long* p) { g_sfm_trace = p; }
-extern "C" void sfm_debug_set_ablate(int a) { g_sfm_ablate = a; }
-#endif
 
 // Launches the tensor-core row step for one chunk as a persistent grid.  `status` is a device int the
 // kernel sets on an internal timeout.
@@ -520,10 +475,6 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v 
     rp.tiles = (p.na + rp.groups_per_tile - 1) / rp.groups_per_tile;
     rp.n_units = p.nbh * rp.tiles * p.blk.b1 * p.fsplit;
     rp.status = status;
-#ifdef SFM_TRACE
-    rp.trace = g_sfm_trace;
-    rp.ablate = g_sfm_ablate;
-#endif
     dim3 grid(rp.n_units < num_sms ? rp.n_units : num_sms);
     // wide blocks: two 64 KB K / V stages instead of five 32 KB ones
     const int smem_bytes = n_s > 64 ? 1024 + kQBytes + 2 * 2 * kStageBytes + 256 : kSmemBytes;

@@ -38,17 +38,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\n"
-#ifdef SFM_TEST_WAIT
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#else
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#endif
             "selp.u32 %0, 1, 0, p;\n}"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-#ifdef SFM_POLL_SLEEP
-        __nanosleep(SFM_POLL_SLEEP);
-#endif
     }
     return false;
 }

@@ -2,8 +2,8 @@
 
 Every function here launches hand-written sm_100a kernels through the C ABI on the current
 CUDA stream.  Inputs must be CUDA bf16 tensors with head_dim 128; anything else raises (there
-is no eager / CPU fallback).  Scratch memory is a per-device buffer that grows on demand and
-is reused by later calls on the same stream order (the reference is single-stream too).
+is no eager / CPU fallback).  Scratch memory is a buffer per (GPU, stream) that grows on demand, is
+reused by later calls queued on that stream and can be dropped with release_workspaces().
 """
 from __future__ import annotations
 
@@ -53,15 +53,29 @@ def _batch_stride(t: torch.Tensor) -> int:
     return t.stride(0) if t.shape[0] > 1 else t.shape[1] * t.shape[2] * t.shape[3]
 
 
+_MAX_WORKSPACES = 8
+
+
 def _workspace(device: torch.device, nbytes: int, tag: str = "monarch") -> torch.Tensor:
-    """Scratch for the row-step results, cached per (GPU, stream): calls queued on one stream run in order
-    and may share it, calls on different streams may overlap and must not."""
+    """Scratch for the row-step results, cached per (GPU, stream, kind): calls queued on one stream run in
+    order and may share it, calls on different streams may overlap and must not.  A buffer only grows (up to
+    the bridge budget, 1 GiB by default, plus the call's fixed part); at most _MAX_WORKSPACES buffers are kept,
+    the least recently used one is dropped beyond that (a buffer was allocated on the stream that uses it, so
+    PyTorch's allocator hands its memory out again in that stream's order only), and release_workspaces()
+    drops them all."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), int(_stream().value or 0), tag)
-    ws = _workspaces.get(key)
+    ws = _workspaces.pop(key, None)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    _workspaces[key] = ws                          # re-inserted last: dict order is the LRU order
+    while len(_workspaces) > _MAX_WORKSPACES:
+        _workspaces.pop(next(iter(_workspaces)))       # freed in the order of the stream it was allocated on
     return ws
+
+
+def release_workspaces() -> None:
+    """Drops every cached scratch buffer (they come back on demand)."""
+    _workspaces.clear()
 
 
 _WATCH_EVERY = 32
@@ -97,8 +111,11 @@ def check_device_status(device=None) -> None:
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     key = (dev.index if dev.index is not None else torch.cuda.current_device(), int(_stream().value or 0), "monarch")
     ws = _workspaces.get(key)                      # the workspace of the current stream
-    if ws is not None:
-        _lib.check(_lib.load().sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        if ws is not None:
+            _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
+        _lib.check(lib.sfm_dense_status(_stream()), "sfm_dense_status")
 
 
 def _rope_table_from_freqs(freqs: Optional[torch.Tensor], device: torch.device) -> torch.Tensor:
@@ -515,6 +532,8 @@ def flash_attention(q, k, v, q_lens=None, k_lens=None, dropout_p=0., softmax_sca
     rc = _lib.load().sfm_dense_fwd(_ptr(q), _batch_stride(q), _ptr(k), _ptr(v), _batch_stride(k), _ptr(out), B, H, D,
                                    n_q, k.shape[1], float(softmax_scale), _stream())
     _lib.check(rc, "sfm_dense_fwd")
+    if os.environ.get("SFM_CHECK_STATUS") == "1":      # debugging aid: synchronises the stream
+        _lib.check(_lib.load().sfm_dense_status(_stream()), "sfm_dense_status")
     return out.type(out_dtype)
 
 

@@ -621,3 +621,43 @@ def test_two_streams_use_separate_workspaces(sfb):
     assert len(keys) == 2
     for o in outs:
         assert torch.equal(o, ref)
+
+
+@pytest.mark.gpu
+def test_recycled_workspace_does_not_raise_a_false_status(sfb):
+    """A workspace that holds garbage (recycled allocator memory) must not read as a failed call: every path,
+    the iterative one included, clears the status word before its first launch."""
+    import ctypes as C
+    from self_forcing_b200 import _lib
+    lib = _lib.load()
+    c = small_case(0, 2)
+    B, n_q, H, D = c["q"].shape
+    ft, hr, wr, h, w = c["blocking"]
+    n_kv = c["n_kv"]
+    kc, vc = c["kbuf"].cuda()[:, :n_kv].contiguous(), c["vbuf"].cuda()[:, :n_kv].contiguous()
+    q = c["q"].cuda()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    for iters in (2, 1):
+        nbytes = lib.sfm_monarch_workspace_bytes(B, H, D, n_q, n_kv, ft, hr, wr, h, w, iters, 0)
+        ws = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device="cuda")
+        out = torch.empty_like(q)
+        rc = lib.sfm_monarch_fwd(ptr(q), n_q * H * D, ptr(kc), ptr(vc), n_kv * H * D, ptr(out), ptr(ws), nbytes, B, H, D,
+                                 n_q, n_kv, ft, hr, wr, h, w, D ** -0.5, iters, 0, stream)
+        assert rc == 0
+        assert lib.sfm_workspace_status(ptr(ws), stream) == 0
+        ref = sfb.ops.monarch_attention_on_cache(q, kc, vc, ft, hr, wr, h, w, num_iters=iters)
+        assert torch.equal(out, ref)
+
+
+@pytest.mark.gpu
+def test_dense_status_word_is_read_and_cleared(sfb):
+    """check_device_status covers the dense kernels' status word: healthy calls leave it at zero."""
+    import ctypes as C
+    from self_forcing_b200 import _lib, ops
+    lib = _lib.load()
+    q = torch.randn(1, 256, 2, 128, device="cuda").bfloat16()
+    sfb.attention(q, q, q)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.sfm_dense_status(stream) == 0
+    ops.check_device_status()
