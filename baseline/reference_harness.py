@@ -162,9 +162,10 @@ def build_generator(model: str = "1.3b", device="cuda", dtype=None, seed: int = 
     shape = dict(MODEL_SHAPES[model]) if isinstance(model, str) else dict(model)
     shape.update(overrides)
     torch.manual_seed(seed)
-    net = CausalWanModel(model_type="t2v", patch_size=(1, 2, 2), text_len=512, in_dim=16, freq_dim=256, text_dim=4096,
-                         out_dim=16, qk_norm=True, cross_attn_norm=True, eps=1e-6, **shape)
-    nn.init.normal_(net.head.head.weight, std=0.02)
+    with torch.device(device):                       # initialise on the target device (14B on the host takes minutes)
+        net = CausalWanModel(model_type="t2v", patch_size=(1, 2, 2), text_len=512, in_dim=16, freq_dim=256,
+                             text_dim=4096, out_dim=16, qk_norm=True, cross_attn_norm=True, eps=1e-6, **shape)
+        nn.init.normal_(net.head.head.weight, std=0.02)
     net = net.to(device=device, dtype=dtype).eval().requires_grad_(False)
     gen = object.__new__(WanDiffusionWrapper)
     nn.Module.__init__(gen)
@@ -196,7 +197,7 @@ class IdentityVAE:
 
 
 def build_pipeline(model: str = "1.3b", blocking: str = "framewise", device="cuda", dtype=None, num_iters: int = 1,
-                   dense_init: bool = False, seed: int = 0, **overrides):
+                   dense_init: bool = False, seed: int = 0, sequence_parallel: bool = False, **overrides):
     """``CausalInferencePipeline`` (pipeline/causal_inference.py:13-49) with the 4-step schedule of the
     reference's inference configs.  The Monarch environment is set before the model is constructed
     (it is read in ``CausalWanSelfAttention.__init__``)."""
@@ -210,11 +211,28 @@ def build_pipeline(model: str = "1.3b", blocking: str = "framewise", device="cud
     from pipeline.causal_inference import CausalInferencePipeline
     dtype = dtype or torch.bfloat16
     gen = build_generator(model, device=device, dtype=dtype, seed=seed, **overrides)
+    if sequence_parallel:
+        # one video over all ranks: tokens sharded outside attention, heads inside (weights replicated);
+        # the reference's wrapper and pipeline stay as they are, the model object is wrapped
+        import torch.distributed as dist
+        from self_forcing_b200.sequence_parallel import (SequenceParallelCausalWan, SequenceParallelModelAdapter,
+                                                         head_sharded_kv_cache)
+        ft = 1 if BLOCKING_ENV[blocking].get("MONARCH_ATTN_FRAMEWISE") == "1" else 3
+        blk = (ft, int(BLOCKING_ENV[blocking].get("MONARCH_ATTN_H_REDUCE", 1)),
+               int(BLOCKING_ENV[blocking].get("MONARCH_ATTN_W_REDUCE", 1)))
+        net = gen.model
+        gen.model = SequenceParallelModelAdapter(net, SequenceParallelCausalWan(net, blk, num_iters=num_iters))
     args = SimpleNamespace(denoising_step_list=[1000, 750, 500, 250], warp_denoising_step=True,
                            independent_first_frame=False, num_frame_per_block=3, context_noise=0)
     with contextlib.redirect_stdout(io.StringIO()):
         pipe = CausalInferencePipeline(args, device, generator=gen, text_encoder=RandomTextEncoder(device, dtype),
                                        vae=IdentityVAE())
+    if sequence_parallel:
+        from utils.resolution import total_seq_len
+
+        def _initialize_kv_cache(batch_size, dtype, device, _pipe=pipe):
+            _pipe.kv_cache1 = head_sharded_kv_cache(net, batch_size, total_seq_len, dist.get_world_size(), device, dtype)
+        pipe._initialize_kv_cache = _initialize_kv_cache
     return pipe
 
 
@@ -229,6 +247,11 @@ def run_rollout(pipe, batch: int = 1, frames: int = 21, seed: int = 2, device="c
     dtype = dtype or torch.bfloat16
     g = torch.Generator(device="cpu").manual_seed(seed)
     noise = torch.randn(batch, frames, 16, 60, 104, generator=g).to(device=device, dtype=dtype)
+    # the pipeline re-seeds the noise it adds between denoising steps from a list walked by a module-level
+    # counter (pipeline/causal_inference.py:10-11, 213-214): start every rollout at its beginning
+    mod = sys.modules.get(type(pipe).__module__)
+    if mod is not None and hasattr(mod, "seed_count"):
+        mod.seed_count = 0
     buf = io.StringIO()
     with contextlib.redirect_stdout(buf), torch.no_grad():
         video, latents = pipe.inference(noise=noise, text_prompts=["synthetic"] * batch, return_latents=True,
@@ -237,3 +260,63 @@ def run_rollout(pipe, batch: int = 1, frames: int = 21, seed: int = 2, device="c
     blocks = [float(m.group(2)) for m in _BLOCK_RE.finditer(text)]
     diff = _DIFF_RE.search(text)
     return latents, {"block_ms": blocks, "diffusion_ms": float(diff.group(1)) if diff else None}
+
+
+def allocate_caches(gen, batch: int, device, dtype, cache_frames: int = 21):
+    """Per-layer KV and cross-attention caches in the pipelines' layout
+    (pipeline/causal_inference.py:288-321, pipeline/causal_diffusion_inference.py:272-330)."""
+    import torch
+    from utils.resolution import frame_height, frame_width
+    net = gen.model
+    heads, hd = net.num_heads, net.dim // net.num_heads
+    n = cache_frames * frame_height * frame_width
+    kv = [{"k": torch.zeros(batch, n, heads, hd, dtype=dtype, device=device),
+           "v": torch.zeros(batch, n, heads, hd, dtype=dtype, device=device),
+           "global_end_index": torch.tensor([0], dtype=torch.long, device=device),
+           "local_end_index": torch.tensor([0], dtype=torch.long, device=device)} for _ in range(net.num_layers)]
+    cross = [{"k": torch.zeros(batch, 512, heads, hd, dtype=dtype, device=device),
+              "v": torch.zeros(batch, 512, heads, hd, dtype=dtype, device=device), "is_init": False}
+             for _ in range(net.num_layers)]
+    return kv, cross
+
+
+def run_cfg_rollout(gen, frames: int = 6, solver_steps: int = 3, guidance_scale: float = 3.0, batch: int = 1,
+                    seed: int = 5, device="cuda", dtype=None):
+    """The call pattern of the reference's many-step sampler with classifier-free guidance
+    (pipeline/causal_diffusion_inference.py:100-262) around the reference's own generator: two KV caches
+    and two cross-attention caches (conditional / unconditional), per chunk ``solver_steps`` times a
+    conditional and an unconditional forward at the same cache position, then one clean-context forward into
+    each cache.  The solver itself (UniPC there) is replaced by a plain Euler step of the flow: it is scalar
+    arithmetic on the latents and does not touch the attention path.  Returns (latents, kv_pos, kv_neg)."""
+    import torch
+    from utils.resolution import frame_height, frame_width
+    dtype = dtype or torch.bfloat16
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    noise = torch.randn(batch, frames, 16, 60, 104, generator=g).to(device=device, dtype=dtype)
+    enc = RandomTextEncoder(device, dtype, seed=seed + 1)
+    cond = enc(["synthetic"] * batch)
+    uncond = RandomTextEncoder(device, dtype, seed=seed + 2)(["negative"] * batch)
+    kv_pos, cross_pos = allocate_caches(gen, batch, device, dtype)
+    kv_neg, cross_neg = allocate_caches(gen, batch, device, dtype)
+    frame_tokens = frame_height * frame_width
+    out = torch.zeros_like(noise)
+    sigmas = torch.linspace(1.0, 0.0, solver_steps + 1)
+    with torch.no_grad():
+        for c0 in range(0, frames, 3):
+            latents = noise[:, c0:c0 + 3]
+            start = c0 * frame_tokens
+            for i in range(solver_steps):
+                t = torch.full([batch, 3], float(sigmas[i]) * 1000.0, device=device, dtype=torch.float32)
+                f_c, _ = gen(noisy_image_or_video=latents, conditional_dict=cond, timestep=t, kv_cache=kv_pos,
+                             crossattn_cache=cross_pos, current_start=start, cache_start=start)
+                f_u, _ = gen(noisy_image_or_video=latents, conditional_dict=uncond, timestep=t, kv_cache=kv_neg,
+                             crossattn_cache=cross_neg, current_start=start, cache_start=start)
+                flow = f_u + guidance_scale * (f_c - f_u)
+                latents = (latents.float() + (float(sigmas[i + 1]) - float(sigmas[i])) * flow.float()).to(dtype)
+            out[:, c0:c0 + 3] = latents
+            t0 = torch.zeros([batch, 3], device=device, dtype=torch.float32)
+            gen(noisy_image_or_video=latents, conditional_dict=cond, timestep=t0, kv_cache=kv_pos,
+                crossattn_cache=cross_pos, current_start=start, cache_start=start)
+            gen(noisy_image_or_video=latents, conditional_dict=uncond, timestep=t0, kv_cache=kv_neg,
+                crossattn_cache=cross_neg, current_start=start, cache_start=start)
+    return out, kv_pos, kv_neg

@@ -123,6 +123,50 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def bind_host_to_gpu(local_rank: int, world: int):
+    """Best effort, multi-rank runs only: run this rank on the cores of its GPU's NUMA node (its share of them,
+    when several ranks' GPUs hang off one node) and prefer that node for new pages, so that the pinned
+    staging buffers of the end-to-end leg (57.5 MB per step and GPU) are not all served by the memory of
+    one socket.  Whatever the container does not allow is skipped; returns what was applied."""
+    info = {}
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+
+        def node_of(i):
+            pr = torch.cuda.get_device_properties(i)
+            path = f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0/numa_node"
+            return int(Path(path).read_text().strip())
+
+        nodes = [node_of(i) for i in range(world)]
+        node = nodes[local_rank]
+        info["numa_node"] = node
+        cpus = allowed
+        if node >= 0:
+            lst = Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
+            on_node = set()
+            for part in lst.split(","):
+                a, _, b = part.partition("-")
+                on_node.update(range(int(a), int(b or a) + 1))
+            if on_node & set(allowed):
+                cpus = sorted(on_node & set(allowed))
+        peers = [r for r in range(world) if nodes[r] == node] if cpus is not allowed else list(range(world))
+        share = max(1, len(cpus) // len(peers))
+        mine = cpus[peers.index(local_rank) * share:(peers.index(local_rank) + 1) * share] or cpus
+        os.sched_setaffinity(0, mine)
+        info["cpus"] = f"{mine[0]}-{mine[-1]} ({len(mine)})"
+        if node >= 0:
+            import ctypes
+            import platform
+            nr = {"x86_64": 238, "aarch64": 237}.get(platform.machine())
+            if nr is not None:
+                mask = ctypes.c_ulong(1 << node)
+                rc = ctypes.CDLL(None, use_errno=True).syscall(nr, 1, ctypes.byref(mask), 64)   # MPOL_PREFERRED
+                info["mempolicy"] = "preferred node" if rc == 0 else f"not applied (errno {ctypes.get_errno()})"
+    except Exception as exc:                                             # sysfs layout, permissions, old torch
+        info["skipped"] = repr(exc)[:120]
+    return info
+
+
 def make_inputs(k: int, seed: int, device, heads: int = HEADS):
     g = torch.Generator(device="cpu").manual_seed(seed)
     mk = lambda n: torch.randn(1, n, heads, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16)
@@ -174,6 +218,19 @@ def time_steps(step, steps, warmup, dist_barrier):
     return e0.elapsed_time(e1)
 
 
+def time_steps_repeated(step, steps, warmup, dist_barrier, min_region_s, reduce_max=None):
+    """The K-step timed loop of time_steps, run as many times back to back as it takes to fill
+    `min_region_s` seconds of timed region (a single 50-step loop of this op lasts a few milliseconds, too
+    short for a stable number or for clock samples).  Every repeat times exactly K steps between barriers;
+    the median repeat is reported.  `reduce_max` turns a local time into the maximum over ranks so that all
+    ranks agree on the number of repeats and on each repeat's time."""
+    red = reduce_max or (lambda x: x)
+    first = red(time_steps(step, steps, warmup, dist_barrier))
+    repeats = max(1, min(2000, int(min_region_s * 1e3 / max(first, 1e-3)) + 1))
+    times = [red(time_steps(step, steps, 0, dist_barrier)) for _ in range(repeats)]
+    return statistics.median(times), repeats, sum(times) * 1e-3
+
+
 def cpu_reference_step(heads_sample: int, blocking: str, k: int, seed: int = 1234):
     """One step of the reference arithmetic on the CPU (fp32, all host threads) for
     `heads_sample` of the heads; returns seconds."""
@@ -202,9 +259,9 @@ def run_reference_arm(args, rank, world):
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    heads_sample = 4
+    heads_sample = HEADS if args.blocking != "dense" else 4      # dense on the CPU: 4 heads per step, scaled
     for _ in range(max(1, min(args.warmup, 2))):
-        cpu_reference_step(heads_sample, args.blocking, args.k)
+        cpu_reference_step(4, args.blocking, args.k)
     t = []
     budget_s, t_start = 150.0, time.perf_counter()
     for _ in range(args.steps):
@@ -221,8 +278,9 @@ def run_reference_arm(args, rank, world):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args),
         "cpu_baseline": {"value": fps, "unit": "latent frames/s", "cores": cores, "kind": "port",
-                         "sample": f"{heads_sample} of {HEADS} heads per step, time scaled x{HEADS // heads_sample}; "
-                                   f"{len(t)} steps; fp32 torch CPU restatement of the reference PyTorch path"},
+                         "sample": (f"the whole step (all {HEADS} heads)" if heads_sample == HEADS else
+                                    f"{heads_sample} of {HEADS} heads per step, time scaled x{HEADS // heads_sample}") +
+                                   f"; {len(t)} steps; fp32 torch CPU restatement of the reference PyTorch path"},
         "e2e": {"value": fps, "unit": "latent frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -315,8 +373,9 @@ def run_model(args, rank, world, device, barrier):
         return
     rh.prepare_imports(root, attention="reference" if args.attention == "reference" else "ours")
     overrides = {"num_layers": args.layers} if args.layers else {}
+    sp = bool(args.sp) and world > 1
     pipe = rh.build_pipeline(args.model, args.blocking, device=device, dense_init=args.dense_init,
-                             num_iters=args.num_iters, seed=rank, **overrides)
+                             num_iters=args.num_iters, seed=0 if sp else rank, sequence_parallel=sp, **overrides)
     if args.attention == "patched":
         import self_forcing_b200 as sfb
         from self_forcing_b200.install import patch_self_attention_forward
@@ -325,7 +384,7 @@ def run_model(args, rank, world, device, barrier):
     from self_forcing_b200 import _lib
     lib = _lib.load() if args.attention != "reference" else None
     for _ in range(max(1, min(args.warmup, 2))):
-        rh.run_rollout(pipe, batch=args.batch, device=device, seed=10 + rank)
+        rh.run_rollout(pipe, batch=args.batch, device=device, seed=10 + (0 if sp else rank))
     torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
@@ -334,7 +393,7 @@ def run_model(args, rank, world, device, barrier):
     diff_ms, block_ms = [], []
     steps = max(1, args.steps)
     for i in range(steps):
-        _, prof = rh.run_rollout(pipe, batch=args.batch, device=device, seed=20 + rank + i)
+        _, prof = rh.run_rollout(pipe, batch=args.batch, device=device, seed=20 + (0 if sp else rank) + i)
         diff_ms.append(prof["diffusion_ms"])
         block_ms.append(prof["block_ms"])
     launches = (lib.sfm_launch_count() - n0) // steps if lib else 0
@@ -349,14 +408,19 @@ def run_model(args, rank, world, device, barrier):
     if rank == 0:
         chunks = [statistics.median(b[i] for b in block_ms) for i in range(len(block_ms[0]))]
         shape = rh.MODEL_SHAPES[args.model]
-        print(json.dumps({**base, "value": 21 * args.batch * world / (ms * 1e-3), "steps": steps,
+        videos = args.batch * (1 if sp else world)
+        if sp:
+            base["scaling"] = "strong"
+        print(json.dumps({**base, "value": 21 * videos / (ms * 1e-3), "steps": steps,
                           "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms, "ms_per_chunk": chunks,
                           "config": {"workload": f"causal Wan-{args.model.upper()} DiT ({shape['num_layers'] if not args.layers else args.layers} blocks, dim "
                                                  f"{shape['dim']}, {shape['num_heads']} heads, FFN {shape['ffn_dim']}), 21x60x104 latent in 7 "
                                                  f"chunks of 3 frames, timesteps [1000, 750, 500, 250] + clean-context pass, "
                                                  f"{args.blocking} self-attention with KV cache, batch {args.batch} per GPU",
                                      "attention": args.attention, "blocking": args.blocking, "batch": args.batch,
-                                     "parallelism": f"dp{world} (independent videos per GPU)"},
+                                     "parallelism": (f"sp{world} (one video over all GPUs: tokens sharded outside attention, heads "
+                                                     "inside, two all-to-alls per layer; weights replicated)") if sp else
+                                                    f"dp{world} (independent videos per GPU)"},
                           "gpu_launches": int(launches), "clocks": clocks}), flush=True)
 
 
@@ -463,7 +527,7 @@ def run_backward(args, sfb, rank, world, device, barrier):
             "clocks": clocks}))
 
 
-def run_ulysses(args, sfb, rank, world, device, barrier):
+def run_ulysses(args, sfb, rank, world, device, barrier, emit=True):
     """Wan-14B self-attention layer (40 heads x 128) on one 3-frame chunk with the heads sharded over
     the ranks: every rank holds 4680/P tokens of q, k, v outside attention and 40/P heads (with their
     KV cache) inside it.  Strong scaling: the total work is fixed."""
@@ -538,9 +602,8 @@ def run_ulysses(args, sfb, rank, world, device, barrier):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total, ms_in, ms_attn, ms_out = (x / args.steps for x in t.tolist())
-    if rank == 0:
-        flops = algorithmic(args.blocking, k, heads=heads)[0]
-        print(json.dumps({
+    flops = algorithmic(args.blocking, k, heads=heads)[0]
+    record = ({
             "metric": "monarch_attn_latent_frames_per_s", "value": CHUNK_FRAMES / (ms_total * 1e-3),
             "unit": "latent frames/s (one Wan-14B attention layer call per 3-frame chunk)",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total,
@@ -551,7 +614,45 @@ def run_ulysses(args, sfb, rank, world, device, barrier):
                                        "two device barriers)") if args.p2p else
                                       f"ulysses{world} (all-to-all q,k,v in; all-to-all out; NCCL)"},
             "split_ms": {"all_to_all_qkv": ms_in, "rope_cache_attention": ms_attn, "all_to_all_out": ms_out},
-            "algorithmic_gflop": flops / 1e9, "clocks": clocks}))
+            "algorithmic_gflop": flops / 1e9, "clocks": clocks})
+    if emit and rank == 0:
+        print(json.dumps(record))
+    return record
+
+
+def ulysses_subrecord(args, sfb, rank, world, device, barrier):
+    """For the multi-GPU default run: the Wan-14B head-sharded attention layer (40 heads over the ranks, strong
+    scaling) on both exchange paths, next to the same 40-head layer call on one GPU alone, so that the record
+    holds the speed-up the head sharding gives at this GPU count."""
+    import copy
+    import torch.distributed as dist
+    a = copy.copy(args)
+    a.steps, a.warmup = min(args.steps, 20), 5
+    sub = {"workload": "Wan-14B self-attention layer call (40 heads x 128, 4680-token chunk vs "
+                       f"{a.k * CHUNK}-token cache, {a.blocking}); strong scaling over {world} GPUs"}
+    # all 40 heads on one GPU (every rank does the same; the slowest counts)
+    g = torch.Generator(device="cpu").manual_seed(77)
+    mk = lambda n: torch.randn(1, n, 40, HEAD_DIM, generator=g).to(torch.bfloat16).to(device)
+    q, kn, vn = mk(CHUNK), mk(CHUNK), mk(CHUNK)
+    n_kv = a.k * CHUNK
+    kc, vc = mk(7 * CHUNK), mk(7 * CHUNK)
+    ft, hr, wr = BLOCKINGS[a.blocking]
+    one = lambda: sfb.rope_monarch_attn_with_kv_cache(q, kn, vn, kc[:, :n_kv], vc[:, :n_kv], n_kv - CHUNK, n_kv,
+                                                      CHUNK_FRAMES * (a.k - 1), ft, hr, wr, H_GRID, W_GRID)
+    t = torch.tensor([time_steps(one, a.steps, a.warmup, barrier) / a.steps], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sub["one_gpu_ms"] = t.item()
+    del q, kn, vn, kc, vc
+    torch.cuda.empty_cache()
+    for name, p2p in (("nccl_all_to_all", False), ("peer_memory", True)):
+        a.p2p = p2p
+        try:
+            r = run_ulysses(a, sfb, rank, world, device, barrier, emit=False)
+            sub[name] = {"ms_per_layer_call": r["ms_per_step"], "speedup_vs_one_gpu": sub["one_gpu_ms"] / r["ms_per_step"],
+                         "efficiency": sub["one_gpu_ms"] / r["ms_per_step"] / world, "split_ms": r["split_ms"]}
+        except (Exception, SystemExit) as exc:
+            sub[name] = {"error": repr(exc)[:200]}
+    return sub
 
 
 def main():
@@ -564,6 +665,8 @@ def main():
     ap.add_argument("--k", type=int, default=7)
     ap.add_argument("--sweep", default=None, help="also time every blocking x k and write a JSON table here")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-region-s", type=float, default=0.5,
+                    help="repeat the timed K-step loop until the timed region is at least this long; report the median repeat")
     ap.add_argument("--ulysses", action="store_true",
                     help="time the Wan-14B attention layer (40 heads) with heads sharded over the GPUs "
                          "(token shards outside attention, two all-to-alls per layer) instead of the headline workload")
@@ -587,6 +690,9 @@ def main():
     ap.add_argument("--attention", default="ours", choices=["ours", "patched", "reference"],
                     help="with --model: what the model's self-attention runs on")
     ap.add_argument("--batch", type=int, default=1, help="with --model: videos per GPU")
+    ap.add_argument("--sp", action="store_true",
+                    help="with --model and N > 1 GPUs: one video over all GPUs (sequence parallel outside attention, head "
+                         "sharding inside) instead of independent videos per GPU")
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the number of blocks (0 = the model's)")
     ap.add_argument("--num-iters", type=int, default=1, help="with --model: MONARCH_ATTN_NUM_ITERS")
     args = ap.parse_args()
@@ -605,6 +711,7 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     use_dist = world > 1
+    host_binding = bind_host_to_gpu(local_rank, world) if use_dist else None
     if use_dist:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
@@ -652,11 +759,22 @@ def main():
     step = make_step(sfb, args.blocking, args.k, qd, kd, vd, caches)
 
     # ---- headline: device-resident inputs -------------------------------------------------
+    def reduce_max(ms):
+        if not use_dist:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    n0 = lib.sfm_launch_count()
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    launches = (lib.sfm_launch_count() - n0) * args.steps // 3      # this library's launches in K steps
     sampler = ClockSampler(local_rank)
     sampler.start()
-    n0 = lib.sfm_launch_count()
-    ms_total = time_steps(step, args.steps, args.warmup, barrier)
-    launches = (lib.sfm_launch_count() - n0) * args.steps // (args.steps + args.warmup)
+    ms_total, repeats, region_s = time_steps_repeated(step, args.steps, args.warmup, barrier, args.min_region_s,
+                                                      reduce_max)
     clocks = sampler.stop()
 
     # ---- per-kernel durations over the same steps (events around every launch) -------------
@@ -685,6 +803,7 @@ def main():
         out_h.copy_(out, non_blocking=True)
 
     ms_e2e_serial = time_steps(e2e_step, args.steps, args.warmup, barrier)
+    ms_e2e_serial = min(ms_e2e_serial, time_steps(e2e_step, args.steps, 0, barrier))
 
     # The same work as a serving loop would issue it: inputs of step i+1 are copied in, and the result of
     # step i-1 is copied out, on two side streams while step i computes (double-buffered device inputs).
@@ -733,12 +852,14 @@ def main():
         barrier()
         return e0.elapsed_time(e1)
 
-    ms_e2e = e2e_run(args.steps, args.warmup)
+    ms_e2e = reduce_max(e2e_run(args.steps, args.warmup))
+    e2e_repeats = max(1, min(200, int(args.min_region_s * 1e3 / max(ms_e2e, 1e-3)) + 1))
+    ms_e2e = statistics.median([reduce_max(e2e_run(args.steps, 0)) for _ in range(e2e_repeats)])
 
     if use_dist:
-        t = torch.tensor([ms_total, ms_e2e, ms_e2e_serial], device=device, dtype=torch.float64)
+        t = torch.tensor([ms_e2e_serial], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e, ms_e2e_serial = t.tolist()
+        ms_e2e_serial = t.item()
 
     ms_step = ms_total / args.steps
     fps = CHUNK_FRAMES * world / (ms_step * 1e-3)
@@ -773,11 +894,15 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args),
         "clocks": clocks,
-        "e2e": {"value": fps_e2e, "unit": "latent frames/s", "ms_per_step": ms_e2e / args.steps,
+        "timing": {"repeats": repeats, "timed_region_s": region_s,
+                   "how": f"median of {repeats} back-to-back repeats of the {args.steps}-step loop (CUDA events, "
+                          "barrier + synchronize around each repeat, max over ranks)"},
+        "e2e": {"value": fps_e2e, "repeats": e2e_repeats, "unit": "latent frames/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": 3 * q.numel() * 2, "d2h_bytes_per_step": q.numel() * 2,
                 "how": "copies of step i+1 / i-1 on side streams while step i computes (double-buffered device inputs)",
                 "serial_ms_per_step": ms_e2e_serial / args.steps},
         "gpu_launches": int(launches),
+        "host_binding": host_binding,
         "kernels": kernels,
         "roofline": roofline,
     }
@@ -785,14 +910,16 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
-        hs = 4
-        cpu_reference_step(hs, args.blocking, args.k)
-        ts = [cpu_reference_step(hs, args.blocking, args.k) for _ in range(3)]
-        sec = statistics.median(ts) * (HEADS / hs)
+        cpu_reference_step(4, args.blocking, args.k)                       # warm-up (thread pool, allocator)
+        ts = [cpu_reference_step(HEADS, args.blocking, args.k) for _ in range(3)]
+        sec = statistics.median(ts)
         line["cpu_baseline"] = {"value": CHUNK_FRAMES / sec, "unit": "latent frames/s", "ms_per_chunk": sec * 1e3,
                                 "cores": cores, "kind": "port",
-                                "sample": f"{hs} of {HEADS} heads, median of 3, time scaled x{HEADS // hs}; fp32 torch "
-                                          "CPU restatement of the reference PyTorch path"}
+                                "sample": f"the whole step (all {HEADS} heads), median of 3; fp32 torch CPU restatement "
+                                          "of the reference PyTorch path (RoPE in fp64 + Monarch reference op)"}
+
+    if use_dist and 40 % world == 0 and CHUNK % world == 0 and os.environ.get("SFM_BENCH_NO_ULYSSES") != "1":
+        line["ulysses"] = ulysses_subrecord(args, sfb, rank, world, device, barrier)
 
     if args.sweep and rank == 0:
         table = []

@@ -223,6 +223,25 @@ int sfm_norm_rope_cache_write(const void* q, const void* k, const void* v,
                               int start_frame, int monarch_order, void* stream);
 
 /*
+ * sfm_norm_rope_cache_write (the norm weights may both be null: no normalisation) with the sliding
+ * window's eviction folded into the same launch: before the new tokens are written at start_idx, the cached
+ * tokens of [roll_dst + roll_shift, start_idx + roll_shift) move left by roll_shift positions (in place, no
+ * temporary; roll_shift = 0 moves nothing).  Requires roll_dst <= start_idx and roll_shift <= n_new, which
+ * hold whenever a full window evicts to make room for a new chunk.  Positions are relative to the cache
+ * pointers given; roll_dst may be negative when those point into the middle of the cache buffer.
+ * Replaces: the shift of the cache after the sink tokens, done through a cloned slice
+ * (wan/modules/causal_model.py:912-926), together with the write that follows it.
+ */
+int sfm_rope_cache_write_roll(const void* q, const void* k, const void* v,
+                              const void* norm_q_weight, const void* norm_k_weight, float eps,
+                              void* q_out, void* k_cache, void* v_cache,
+                              int64_t cache_batch_stride, const float* rope,
+                              int B, int n_new, int H, int D, int start_idx,
+                              int roll_dst, int roll_shift,
+                              int f_tied, int h_reduce, int w_reduce, int h, int w,
+                              int start_frame, int monarch_order, void* stream);
+
+/*
  * Head-sharded attention across the GPUs of one box (Ulysses style), with the exchange done by
  * the kernels themselves over peer memory instead of two all-to-all collectives.
  *

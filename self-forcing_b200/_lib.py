@@ -32,6 +32,8 @@ SIGNATURES = {
     "sfm_static_scratch_bytes": (C.c_size_t, []),
     "sfm_norm_rope_cache_write": (C.c_int, [C.c_void_p] * 5 + [C.c_float] + [C.c_void_p] * 3 + [C.c_int64, C.c_void_p] +
                                   [C.c_int] * 12 + [C.c_void_p]),
+    "sfm_rope_cache_write_roll": (C.c_int, [C.c_void_p] * 5 + [C.c_float] + [C.c_void_p] * 3 + [C.c_int64, C.c_void_p] +
+                                  [C.c_int] * 14 + [C.c_void_p]),
     "sfm_rope_cache_write_gather": (C.c_int, [C.c_void_p] * 3 + [C.c_int, C.c_int] + [C.c_void_p] * 3 +
                                     [C.c_int64, C.c_void_p] + [C.c_int] * 12 + [C.c_void_p]),
     "sfm_monarch_fwd_scatter": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,

@@ -16,6 +16,14 @@ namespace sfm {
 // then lives in buffer n / src_tokens, a [B, src_tokens, src_heads, 128] tensor of which this GPU takes
 // heads [head0, head0 + H).  Buffers of other GPUs are read with plain loads over NVLink.  Unsharded
 // input is the case of one buffer with src_tokens = n_new, src_heads = H, head0 = 0.
+//
+// Sliding-window eviction (causal_model.py:912-926) can ride along: before the new tokens land, the cached
+// tokens after the sink move left by `roll_shift` positions, cache[p] = cache[p + roll_shift] for
+// roll_dst <= p < start_idx, and the new tokens follow them at start_idx.  The move overlaps itself, but it
+// splits into independent chains p, p + shift, p + 2 shift, ... one per residue of p; the chain that ends at
+// position start_idx + m is walked, front to back, by the CTA that afterwards writes the new token of slot
+// m < shift there (every element is read before the same thread overwrites it), so the whole eviction needs
+// no temporary and no ordering between CTAs.
 struct PeerSrc {
     const uint4* q[kMaxPeers];
     const uint4* k[kMaxPeers];
@@ -24,11 +32,12 @@ struct PeerSrc {
 
 __global__ void __launch_bounds__(256)
 rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int src_heads, int head0,
-                        uint4* __restrict__ q_out, uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
+                        uint4* __restrict__ q_out, uint4* k_cache, uint4* v_cache,
                         long long cache_batch_stride_vec, const float2* __restrict__ rope,
                         int B, int n_new, int H, int start_idx, Blocking blk, int start_frame,
                         int monarch_order, int p0, int p1,
-                        const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, float eps) {
+                        const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, float eps,
+                        int roll_dst, int roll_shift) {
     constexpr int kVecPerRow = kHeadDim / 8;  // 16
     __shared__ float2 cs_s[kHeadDim / 2];
     __shared__ float red_s[2][8];
@@ -93,6 +102,22 @@ rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int
             __syncthreads();
         }
         const long long dst_row = (long long)b * cache_batch_stride_vec + (long long)dst_tok * H * kVecPerRow;
+        if (roll_shift > 0 && dst_tok - start_idx < roll_shift) {
+            // this token's slot ends a chain of the eviction shift: walk it (same thread-to-vector mapping as
+            // the write below, so the last source element is read by the thread that then overwrites it)
+            const long long tok_vecs = (long long)H * kVecPerRow;
+            const long long base = (long long)b * cache_batch_stride_vec;
+            const int first = roll_dst + (dst_tok - roll_dst) % roll_shift;
+            for (int pos = first; pos < dst_tok; pos += roll_shift) {
+                for (int t = threadIdx.x; t < H * kVecPerRow; t += blockDim.x) {
+                    const long long d = base + pos * tok_vecs + t, sidx = d + roll_shift * tok_vecs;
+                    const uint4 kk = k_cache[sidx];
+                    const uint4 vv = v_cache[sidx];
+                    k_cache[d] = kk;
+                    v_cache[d] = vv;
+                }
+            }
+        }
         for (int t = threadIdx.x; t < H * kVecPerRow; t += blockDim.x) {
             const int vec = t & (kVecPerRow - 1);
             const long long idx = src_vec0 + t;
@@ -194,7 +219,7 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
                           void* k_cache, void* v_cache, int64_t cache_batch_stride, const float* rope, int B, int n_new,
                           int H, int D, int start_idx, int f_tied, int h_reduce, int w_reduce, int h, int w,
                           int start_frame, int monarch_order, void* stream, const void* wq = nullptr,
-                          const void* wk = nullptr, float eps = 0.f) {
+                          const void* wk = nullptr, float eps = 0.f, int roll_dst = 0, int roll_shift = 0) {
     if (!k_cache || !v_cache) return SFM_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk)) & 15) return SFM_ERR_ALIGNMENT;
     if (have_q && !q_out) return SFM_ERR_NULL_POINTER;
@@ -211,6 +236,8 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
     auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
     if (mis(q_out) || mis(k_cache) || mis(v_cache) || (cache_batch_stride % 8)) return SFM_ERR_ALIGNMENT;
     if (cache_batch_stride < (int64_t)(start_idx + n_new) * H * D && B > 1) return SFM_ERR_BAD_SHAPE;
+    // eviction shift: the moved tokens end where the new ones start, and every chain ends in a new token's slot
+    if (roll_shift < 0 || (roll_shift > 0 && (roll_dst > start_idx || roll_shift > n_new))) return SFM_ERR_BAD_SHAPE;
     int c = D / 2;
     int p0 = c - 2 * (c / 3), p1 = c / 3;
     int threads = H * (D / 8);
@@ -221,7 +248,7 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
     rope_cache_write_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
         src, src_tokens, src_heads, head0, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache, cache_batch_stride / 8,
         (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0, p1,
-        (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, eps);
+        (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, eps, roll_dst, roll_shift);
     return (int)cudaGetLastError();
 }
 }  // namespace
@@ -256,6 +283,24 @@ extern "C" int sfm_norm_rope_cache_write(const void* q, const void* k, const voi
     return rope_cache_write_impl(src, true, n_new > 0 ? n_new : 1, H, 0, q_out, k_cache, v_cache, cache_batch_stride,
                                  rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w, start_frame,
                                  monarch_order, stream, norm_q_weight, norm_k_weight, eps);
+}
+
+extern "C" int sfm_rope_cache_write_roll(const void* q, const void* k, const void* v, const void* norm_q_weight,
+                                         const void* norm_k_weight, float eps, void* q_out, void* k_cache,
+                                         void* v_cache, int64_t cache_batch_stride, const float* rope, int B,
+                                         int n_new, int H, int D, int start_idx, int roll_dst, int roll_shift,
+                                         int f_tied, int h_reduce, int w_reduce, int h, int w, int start_frame,
+                                         int monarch_order, void* stream) {
+    if (!q || !k || !v) return SFM_ERR_NULL_POINTER;
+    if ((norm_q_weight == nullptr) != (norm_k_weight == nullptr)) return SFM_ERR_NULL_POINTER;
+    if (!(eps >= 0.f)) return SFM_ERR_BAD_SHAPE;
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (mis(q) || mis(k) || mis(v)) return SFM_ERR_ALIGNMENT;
+    PeerSrc src = {};
+    src.q[0] = (const uint4*)q; src.k[0] = (const uint4*)k; src.v[0] = (const uint4*)v;
+    return rope_cache_write_impl(src, true, n_new > 0 ? n_new : 1, H, 0, q_out, k_cache, v_cache, cache_batch_stride,
+                                 rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w, start_frame,
+                                 monarch_order, stream, norm_q_weight, norm_k_weight, eps, roll_dst, roll_shift);
 }
 
 extern "C" int sfm_rope_cache_write_gather(const void* const* q_shards, const void* const* k_shards,

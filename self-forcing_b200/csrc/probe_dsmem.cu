@@ -32,10 +32,10 @@ __global__ void __launch_bounds__(kThreads, 1) dsmem_store_kernel(int iters, int
         unsigned char* base = static_cast<unsigned char*>(cluster.map_shared_rank(static_cast<void*>(buf), dst));
         if (PATTERN == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {                       // lane = row, 8 pieces of 32 bytes
-                volatile uint4* p = reinterpret_cast<volatile uint4*>(base + (size_t)tid * 256 + c * 32);
-                p[0].x = v.x; p[0].y = v.y; p[0].z = v.z; p[0].w = v.w;
-                p[1].x = v.x; p[1].y = v.y; p[1].z = v.z; p[1].w = v.w;
+            for (int c = 0; c < 8; ++c) {                       // lane = row, 8 pieces of 32 bytes (2 x 16-byte stores)
+                uint4* p = reinterpret_cast<uint4*>(base + (size_t)tid * 256 + c * 32);
+                asm volatile("st.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                asm volatile("st.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p + 1), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
             }
         } else {
 #pragma unroll

@@ -11,6 +11,8 @@ Differences from the reference, none of them visible in the results:
   the device tensors ``global_end_index`` / ``local_end_index`` of a reference cache dict are still
   updated when such a dict is adopted with ``KVCache.from_reference``;
 * normalisation, rotation and the cache write are one kernel (`ops.norm_rope_cache_write`);
+* the sliding window's eviction shift (causal_model.py:912-926) runs inside the cache-write kernel when the
+  moved tokens end where the new ones start (a fresh chunk into a full window), else as in-place copies;
 * the new keys / values are written before attention in both branches, as the Monarch branch of the
   reference does (monarch_attn.py:1230-1231); its dense branch writes them at the same place
   (causal_model.py:961-962).
@@ -146,8 +148,15 @@ def self_attention_kv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cache: 
     start_frame = current_start // frame_tokens
     step = plan_cache_step(current_start, n, cache.global_end, cache.local_end, cache.k.shape[1],
                            cfg.max_attention_size, cfg.local_attn_size, cfg.sink_size * frame_tokens)
+    roll = None
     if step.roll is not None:
-        cache._roll(step.roll)
+        dst, src, count = step.roll
+        if count > 0 and dst + count == step.cache_start + step.local_start and src - dst <= n:
+            # the usual case (a fresh chunk evicts from a full window): the moved tokens end where the new
+            # ones start, so the shift rides inside the cache-write kernel; positions relative to the view
+            roll = (dst - step.cache_start, src - dst)
+        else:
+            cache._roll(step.roll)
     curr_k = cache.k[:, step.cache_start:step.cache_start + step.local_end]
     curr_v = cache.v[:, step.cache_start:step.cache_start + step.local_end]
     is_init = cfg.use_dense_init and curr_k.shape[1] == 3 * frame_tokens
@@ -155,7 +164,7 @@ def self_attention_kv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cache: 
     f_tied = 1 if cfg.use_framewise else 3
     q_rot = ops.norm_rope_cache_write(q, k, v, curr_k, curr_v, step.local_start, start_frame, f_tied, cfg.h_reduce,
                                       cfg.w_reduce, gh, gw, freqs=freqs, norm_q_weight=norm_q_weight,
-                                      norm_k_weight=norm_k_weight, eps=cfg.eps, monarch_order=not dense)
+                                      norm_k_weight=norm_k_weight, eps=cfg.eps, monarch_order=not dense, roll=roll)
     if dense:
         out = ops.dense_attention_on_cache(q_rot, curr_k, curr_v, sm_scale)
     else:

@@ -336,11 +336,13 @@ def monarch_attn_with_kv_cache(q, k_cache, v_cache, new_k, new_v, start_idx, end
 
 
 def norm_rope_cache_write(q, k, v, k_cache, v_cache, start_idx, start_frame, f_tied, h_reduce, w_reduce, h, w,
-                          freqs=None, norm_q_weight=None, norm_k_weight=None, eps=1e-6, monarch_order=True):
+                          freqs=None, norm_q_weight=None, norm_k_weight=None, eps=1e-6, monarch_order=True, roll=None):
     """One kernel: optional full-width RMSNorm of q and k (WanRMSNorm, model.py:462-478, as applied in
     qkv_fn, causal_model.py:801-807), 3-axis RoPE with frame offset (causal_model.py:687-715), and the
     in-place write of k, v into cache tokens [start_idx, start_idx + n) in Monarch order (or natural
-    order for the dense branch).  Returns the normalised, rotated q."""
+    order for the dense branch).  ``roll`` = (dst, shift) folds the sliding window's eviction into the same
+    launch: the cached tokens [dst + shift, start_idx + shift) first move left by ``shift``
+    (causal_model.py:912-926).  Returns the normalised, rotated q."""
     for t, name in ((q, "q"), (k, "k"), (v, "v")):
         _require(t, name)
     _cache_view_ok(k_cache, "k_cache")
@@ -354,11 +356,22 @@ def norm_rope_cache_write(q, k, v, k_cache, v_cache, start_idx, start_frame, f_t
     lib = _lib.load()
     if (norm_q_weight is None) != (norm_k_weight is None):
         raise ValueError("give both norm weights or neither")
+    wq = wk = None
     if norm_q_weight is not None:
         wq = norm_q_weight.detach().to(device=q.device, dtype=torch.bfloat16).contiguous()
         wk = norm_k_weight.detach().to(device=q.device, dtype=torch.bfloat16).contiguous()
         if wq.numel() != H * D or wk.numel() != H * D:
             raise ValueError("norm weights must have H*D elements")
+    if roll is not None:
+        dst, shift = int(roll[0]), int(roll[1])
+        if start_idx + shift > k_cache.shape[1]:
+            raise ValueError("the eviction shift reads past the cache view")
+        rc = lib.sfm_rope_cache_write_roll(_ptr(q), _ptr(k), _ptr(v), _ptr(wq), _ptr(wk), float(eps), _ptr(q_rot),
+                                           _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache), _ptr(tab), B, n, H, D,
+                                           int(start_idx), dst, shift, f_tied, h_reduce, w_reduce, h, w,
+                                           int(start_frame), 1 if monarch_order else 0, _stream())
+        _lib.check(rc, "sfm_rope_cache_write_roll")
+    elif norm_q_weight is not None:
         rc = lib.sfm_norm_rope_cache_write(_ptr(q), _ptr(k), _ptr(v), _ptr(wq), _ptr(wk), float(eps), _ptr(q_rot),
                                            _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache), _ptr(tab), B, n, H, D,
                                            int(start_idx), f_tied, h_reduce, w_reduce, h, w, int(start_frame),

@@ -430,18 +430,23 @@ def _oracle_layer_call(state, q, k, v, current_start, grid, cfg, wq, wk):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["plain", "window_sink", "dense_init", "regular"])
+@pytest.mark.parametrize("mode", ["plain", "window_sink", "window10_sink2", "window7_dense", "dense_init", "regular"])
 def test_layer_rollout_matches_oracle(sfb, mode):
     """Several chunks through self_attention_kv (each chunk denoised twice, as the few-step sampler does)
     against the oracle's restatement of the reference layer, including the sliding window with a sink frame,
     the dense first chunk and the all-dense configuration; the caches must agree too."""
-    rng = np.random.default_rng({"plain": 1, "window_sink": 2, "dense_init": 3, "regular": 4}[mode])
+    rng = np.random.default_rng({"plain": 1, "window_sink": 2, "dense_init": 3, "regular": 4, "window10_sink2": 5,
+                                 "window7_dense": 6}[mode])
     B, H, gh, gw = 1, 2, 6, 8
     frame, n = gh * gw, 3 * gh * gw
     cfg = sfb.LayerConfig(use_framewise=True)
     cache_frames = 12
-    if mode == "window_sink":
+    if mode == "window_sink":                      # evicts a whole chunk each time (shift inside the write kernel)
         cfg.local_attn_size, cfg.sink_size, cache_frames = 9, 1, 9
+    if mode == "window10_sink2":                   # window not a multiple of the chunk: the first eviction is shorter
+        cfg.local_attn_size, cfg.sink_size, cache_frames = 10, 2, 10
+    if mode == "window7_dense":                    # natural-order (dense) cache with eviction
+        cfg.local_attn_size, cfg.sink_size, cache_frames, cfg.disable_monarch = 7, 0, 7, True
     if mode == "dense_init":
         cfg.use_dense_init = True
     if mode == "regular":
@@ -452,7 +457,7 @@ def test_layer_rollout_matches_oracle(sfb, mode):
              "g_end": 0, "l_end": 0}
     wq = bf(torch.from_numpy(rng.uniform(0.7, 1.3, size=H * 128).astype(np.float32)))
     wk = bf(torch.from_numpy(rng.uniform(0.7, 1.3, size=H * 128).astype(np.float32)))
-    n_chunks = 6 if mode == "window_sink" else 4
+    n_chunks = 6 if mode.startswith("window") else 4
     for chunk in range(n_chunks):
         for rep in range(2):
             q, k, v = (bf(cases.randn(rng, B, n, H, 128)) for _ in range(3))

@@ -200,3 +200,36 @@ def test_whole_model_rollout_through_the_reference_pipeline(causal_model):
     finally:
         cls.forward = original
     assert _rel_l2(lat2, lat) <= 2e-2
+
+
+@pytest.mark.gpu
+def test_cfg_two_cache_rollout(causal_model):
+    """Classifier-free guidance with two KV caches (the call pattern of the reference's many-step sampler):
+    conditional and unconditional forwards alternate on the same stream at the same cache position, each into
+    its own cache.  The reference's own forward on this package's operators and the patched forward must
+    agree, and both caches must end at the same indices."""
+    from self_forcing_b200.install import patch_self_attention_forward
+    cm = causal_model
+    for k in rh._ENV_KEYS:
+        os.environ.pop(k, None)
+    os.environ.update(rh.BLOCKING_ENV["framewise"])
+    gen = rh.build_generator("1.3b", device="cuda", num_layers=2)
+    lat, kv_pos, kv_neg = rh.run_cfg_rollout(gen, frames=6, solver_steps=3)
+    cls = cm.CausalWanSelfAttention
+    original = cls.forward
+    try:
+        patch_self_attention_forward(cls)
+        lat2, kv_pos2, kv_neg2 = rh.run_cfg_rollout(gen, frames=6, solver_steps=3)
+    finally:
+        cls.forward = original
+    torch.cuda.synchronize()
+    assert torch.isfinite(lat).all() and lat.float().std() > 0
+    assert _rel_l2(lat2, lat) <= 2e-2
+    n = 6 * 30 * 52
+    for a, b in ((kv_pos, kv_pos2), (kv_neg, kv_neg2)):
+        for la, lb in zip(a, b):
+            assert int(la["global_end_index"]) == int(lb["global_end_index"]) == n
+            assert int(la["local_end_index"]) == int(lb["local_end_index"]) == n
+            assert _rel_l2(lb["k"][:, :n], la["k"][:, :n]) <= 5e-3
+    # the two caches hold different keys (different text context flows into the later blocks)
+    assert not torch.equal(kv_pos[1]["k"][:, :n], kv_neg[1]["k"][:, :n])
