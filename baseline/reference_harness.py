@@ -197,7 +197,8 @@ class IdentityVAE:
 
 
 def build_pipeline(model: str = "1.3b", blocking: str = "framewise", device="cuda", dtype=None, num_iters: int = 1,
-                   dense_init: bool = False, seed: int = 0, sequence_parallel: bool = False, **overrides):
+                   dense_init: bool = False, seed: int = 0, sequence_parallel: bool = False,
+                   exchange: str = "all_to_all", **overrides):
     """``CausalInferencePipeline`` (pipeline/causal_inference.py:13-49) with the 4-step schedule of the
     reference's inference configs.  The Monarch environment is set before the model is constructed
     (it is read in ``CausalWanSelfAttention.__init__``)."""
@@ -221,7 +222,8 @@ def build_pipeline(model: str = "1.3b", blocking: str = "framewise", device="cud
         blk = (ft, int(BLOCKING_ENV[blocking].get("MONARCH_ATTN_H_REDUCE", 1)),
                int(BLOCKING_ENV[blocking].get("MONARCH_ATTN_W_REDUCE", 1)))
         net = gen.model
-        gen.model = SequenceParallelModelAdapter(net, SequenceParallelCausalWan(net, blk, num_iters=num_iters))
+        gen.model = SequenceParallelModelAdapter(net, SequenceParallelCausalWan(net, blk, num_iters=num_iters,
+                                                                                   exchange=exchange))
     args = SimpleNamespace(denoising_step_list=[1000, 750, 500, 250], warp_denoising_step=True,
                            independent_first_frame=False, num_frame_per_block=3, context_noise=0)
     with contextlib.redirect_stdout(io.StringIO()):

@@ -375,7 +375,8 @@ def run_model(args, rank, world, device, barrier):
     overrides = {"num_layers": args.layers} if args.layers else {}
     sp = bool(args.sp) and world > 1
     pipe = rh.build_pipeline(args.model, args.blocking, device=device, dense_init=args.dense_init,
-                             num_iters=args.num_iters, seed=0 if sp else rank, sequence_parallel=sp, **overrides)
+                             num_iters=args.num_iters, seed=0 if sp else rank, sequence_parallel=sp,
+                             exchange="peer" if args.p2p else "all_to_all", **overrides)
     if args.attention == "patched":
         import self_forcing_b200 as sfb
         from self_forcing_b200.install import patch_self_attention_forward
@@ -419,7 +420,8 @@ def run_model(args, rank, world, device, barrier):
                                                  f"{args.blocking} self-attention with KV cache, batch {args.batch} per GPU",
                                      "attention": args.attention, "blocking": args.blocking, "batch": args.batch,
                                      "parallelism": (f"sp{world} (one video over all GPUs: tokens sharded outside attention, heads "
-                                                     "inside, two all-to-alls per layer; weights replicated)") if sp else
+                                                     f"inside, exchanged {'by the kernels over peer memory' if args.p2p else 'by two all-to-alls'} per layer; "
+                                                     "weights replicated)") if sp else
                                                     f"dp{world} (independent videos per GPU)"},
                           "gpu_launches": int(launches), "clocks": clocks}), flush=True)
 
@@ -677,7 +679,8 @@ def main():
                     help="time forward + backward of the attention op at the headline shape instead of the headline workload")
     ap.add_argument("--dense-init", action="store_true", help="with --rollout: dense attention for the first chunk")
     ap.add_argument("--p2p", action="store_true",
-                    help="with --ulysses: the kernels gather / scatter over peer memory instead of the two NCCL all-to-alls")
+                    help="with --ulysses or --model --sp: the kernels gather / scatter over peer memory instead of the two "
+                         "NCCL all-to-alls")
     ap.add_argument("--probe-dsmem", action="store_true",
                     help="measure store bandwidth between the CTAs of a cluster (distributed shared memory) and exit")
     ap.add_argument("--incumbent", action="store_true",

@@ -5,7 +5,7 @@
 // (head, query group) over the CTAs of a cluster and writing each row into the shared memory of the CTA that
 // owns its column.  This probe measures the ceiling of that traffic pattern on the device at hand: every CTA
 // of every cluster streams 256-byte rows into its peers' shared memory with plain stores through
-// cluster-mapped addresses (no multicast, no TMA), in the epilogue's access pattern (one row per lane, 32
+// cluster-mapped addresses (ordinary st instructions only), in the epilogue's access pattern (one row per lane, 32
 // bytes per store) and fully coalesced (consecutive lanes, 16 bytes each).
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>

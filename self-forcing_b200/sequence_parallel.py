@@ -11,8 +11,8 @@ apply the per-frame modulation (``x.shape[1] // e.shape[1]``, wan/modules/causal
 :1233-1235), and S/P tokens are not a whole number of frames.  ``SequenceParallelCausalWan`` re-states
 ``CausalWanModel._forward_inference`` (:1582-1720), ``CausalWanAttentionBlock.forward`` (:1152-1205) and
 ``CausalHead.forward`` (:1225-1236) around the model's OWN sub-modules and parameters with the modulation
-looked up per token (``e[:, token // tokens_per_frame]``), which is the same arithmetic element for
-element; nothing in the model object is modified.  The only precedent in the reference is the xfuser
+looked up per token (``e[:, token // tokens_per_frame]``, applied frame piece by frame piece as broadcasts),
+which is the same arithmetic element for element; nothing in the model object is modified.  The only precedent in the reference is the xfuser
 wrapper for the bidirectional model (wan/distributed/xdit_context_parallel.py:66-146: chunk after the
 embeddings, all-gather after the head).
 
@@ -66,12 +66,18 @@ class SequenceParallelCausalWan:
     RoPE + cache write + Monarch attention.  ``blocking`` = (f_tied, h_reduce, w_reduce); the token grid comes
     from the input."""
 
-    def __init__(self, model, blocking=(1, 1, 1), group=None, attn_fn: Optional[Callable] = None, num_iters: int = 1):
+    def __init__(self, model, blocking=(1, 1, 1), group=None, attn_fn: Optional[Callable] = None, num_iters: int = 1,
+                 exchange: str = "all_to_all"):
+        if exchange not in ("all_to_all", "peer"):
+            raise ValueError("exchange must be 'all_to_all' (NCCL / gloo collectives) or 'peer' (the kernels gather "
+                             "and scatter over peer memory; GPUs of one box, single-pass Monarch only)")
         self.model = model
         self.group = group
         self.blocking = tuple(blocking)
         self.attn_fn = attn_fn
         self.num_iters = num_iters
+        self.exchange = exchange
+        self._peer = None
         self.world, self.rank = _world(group), _rank(group)
         if model.num_heads % self.world:
             raise ValueError(f"{model.num_heads} heads do not divide over {self.world} ranks")
@@ -107,26 +113,54 @@ class SequenceParallelCausalWan:
                                cache.k.shape[1])
         if step.roll is not None or step.cache_start != 0:
             raise NotImplementedError("sequence parallelism runs with the global attention window")
-        if self._ulysses is None:
-            self._ulysses = UlyssesSelfAttention(self.blocking + (gh, gw), self.group, self.attn_fn, self.num_iters)
-        out = self._ulysses(q, k, v, cache.k, cache.v, step.local_start, step.local_end,
-                            start_frame=current_start // (gh * gw))
+        start_frame = current_start // (gh * gw)
+        if self.exchange == "peer" and self.world > 1:
+            if self._peer is None or self._peer.shape != (b, sp, n, d):
+                from .ulysses import PeerShardedSelfAttention
+                self._peer = PeerShardedSelfAttention(self.blocking + (gh, gw), b, n_new, n, h.device, self.group)
+            self._peer.q_in.copy_(q)
+            self._peer.k_in.copy_(k)
+            self._peer.v_in.copy_(v)
+            out = self._peer(cache.k, cache.v, step.local_start, step.local_end, start_frame)
+        else:
+            if self._ulysses is None:
+                self._ulysses = UlyssesSelfAttention(self.blocking + (gh, gw), self.group, self.attn_fn, self.num_iters)
+            out = self._ulysses(q, k, v, cache.k, cache.v, step.local_start, step.local_end, start_frame=start_frame)
         cache._store(step)
         return attn.o(out.flatten(2))
 
-    def _block(self, block, x, e_tok, grid, context, context_lens, cache, crossattn_cache, current_start):
-        """CausalWanAttentionBlock.forward with e_tok = per-token modulation [B, S/P, 6, C]."""
-        e = (block.modulation.unsqueeze(1) + e_tok).unbind(dim=2)      # modulation [1, 6, C] -> [1, 1, 6, C]
-        y = self._self_attention(block.self_attn, block.norm1(x) * (1 + e[1]) + e[0], cache, current_start, grid)
-        x = x + y * e[2]
-        x = x + block.cross_attn(block.norm3(x), context, context_lens, crossattn_cache=crossattn_cache)
-        y = block.ffn(block.norm2(x) * (1 + e[4]) + e[3])
-        return x + y * e[5]
+    @staticmethod
+    def _modulate(x, scale, shift, segments):
+        """x * (1 + scale[frame of token]) + shift[frame of token] without materialising per-token factors: a token
+        slice covers a few whole or partial frames, each handled as one broadcast over its tokens.
+        scale, shift: [B, F, C]; segments: [(first token, end token, frame)] of this rank's slice."""
+        out = torch.empty_like(x)
+        for t0, t1, f in segments:
+            torch.addcmul(shift[:, f:f + 1], x[:, t0:t1], 1 + scale[:, f:f + 1], out=out[:, t0:t1])
+        return out
 
-    def _head(self, head, x, e_tok):
-        """CausalHead.forward with e_tok = per-token embedding [B, S/P, 1, C]."""
-        e = (head.modulation.unsqueeze(1) + e_tok).unbind(dim=2)
-        return head.head(head.norm(x) * (1 + e[1]) + e[0])
+    @staticmethod
+    def _gated_add(x, y, gate, segments):
+        """x + y * gate[frame of token], same segment-wise broadcast."""
+        out = torch.empty_like(x)
+        for t0, t1, f in segments:
+            torch.addcmul(x[:, t0:t1], y[:, t0:t1], gate[:, f:f + 1], out=out[:, t0:t1])
+        return out
+
+    def _block(self, block, x, e0, segments, grid, context, context_lens, cache, crossattn_cache, current_start):
+        """CausalWanAttentionBlock.forward on a token slice; e0 = per-frame time projection [B, F, 6, C]."""
+        e = (block.modulation.unsqueeze(1) + e0).unbind(dim=2)         # six [B, F, C], as in the reference
+        y = self._self_attention(block.self_attn, self._modulate(block.norm1(x), e[1], e[0], segments), cache,
+                                 current_start, grid)
+        x = self._gated_add(x, y, e[2], segments)
+        x = x + block.cross_attn(block.norm3(x), context, context_lens, crossattn_cache=crossattn_cache)
+        y = block.ffn(self._modulate(block.norm2(x), e[4], e[3], segments))
+        return self._gated_add(x, y, e[5], segments)
+
+    def _head(self, head, x, e, segments):
+        """CausalHead.forward on a token slice; e = per-frame time embedding [B, F, 1, C]."""
+        e = (head.modulation.unsqueeze(1) + e).unbind(dim=2)           # two [B, F, C]
+        return head.head(self._modulate(head.norm(x), e[1], e[0], segments))
 
     # ------------------------------------------------------------------------------ forward
     def forward(self, x, t, context, kv_caches: List[KVCache], crossattn_caches: List[dict], current_start: int = 0):
@@ -152,12 +186,16 @@ class SequenceParallelCausalWan:
 
         x = shard_tokens(x, self.group)
         sp = x.shape[1]
-        frame_of_token = (torch.arange(sp, device=x.device) + self.rank * sp) // frame_tokens
-        e_tok = e0.index_select(1, frame_of_token)                                # [B, S/P, 6, C]
+        # this rank's tokens [rank * sp, (rank + 1) * sp) cut at frame boundaries: (first, end, frame) per piece
+        segments, g0 = [], self.rank * sp
+        while g0 < (self.rank + 1) * sp:
+            f = g0 // frame_tokens
+            g1 = min((f + 1) * frame_tokens, (self.rank + 1) * sp)
+            segments.append((g0 - self.rank * sp, g1 - self.rank * sp, f))
+            g0 = g1
         for i, block in enumerate(m.blocks):
-            x = self._block(block, x, e_tok, grid, context, None, kv_caches[i], crossattn_caches[i], current_start)
-        e_head = e.unflatten(dim=0, sizes=t.shape).unsqueeze(2).index_select(1, frame_of_token)   # [B, S/P, 1, C]
-        x = self._head(m.head, x, e_head)
+            x = self._block(block, x, e0, segments, grid, context, None, kv_caches[i], crossattn_caches[i], current_start)
+        x = self._head(m.head, x, e.unflatten(dim=0, sizes=t.shape).unsqueeze(2), segments)
         x = gather_tokens(x, self.group)
         return torch.stack(m.unpatchify(x, grid_sizes))
 

@@ -163,8 +163,8 @@ def _sp_worker(rank, world, port, result_dir):
         hd = slice(rank * 2, rank * 2 + 2)
         for layer in range(2):
             assert kv_sp[layer].global_end == int(kv_ref[layer]["global_end_index"]) == 6 * frame
-            np.testing.assert_allclose(kv_sp[layer].k.numpy(), kv_ref[layer]["k"][:, :, hd].numpy(), rtol=1e-5, atol=1e-6)
-            np.testing.assert_allclose(kv_sp[layer].v.numpy(), kv_ref[layer]["v"][:, :, hd].numpy(), rtol=1e-5, atol=1e-6)
+            np.testing.assert_allclose(kv_sp[layer].k.numpy(), kv_ref[layer]["k"][:, :, hd].numpy(), rtol=2e-4, atol=2e-5)
+            np.testing.assert_allclose(kv_sp[layer].v.numpy(), kv_ref[layer]["v"][:, :, hd].numpy(), rtol=2e-4, atol=2e-5)
         Path(result_dir, f"sp_ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()
