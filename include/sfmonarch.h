@@ -242,6 +242,21 @@ int sfm_rope_cache_write_roll(const void* q, const void* k, const void* v,
                               int start_frame, int monarch_order, void* stream);
 
 /*
+ * Normalisation and rotation of a token SLICE of a chunk, for sequence-parallel callers that hold n_tokens
+ * consecutive tokens starting at token0 of the chunk's (frames, h, w) grid: q_out, k_out <- RoPE(RMSNorm(q, k))
+ * with each token's true grid position, v_out <- v, all [B, n_tokens, H, D] in natural order (the outputs may be
+ * the buffers another GPU's sfm_rope_cache_write_gather reads, which then runs without a rotation table).
+ * The norm weights may both be null (rotation only).
+ * Replaces: norm_q / norm_k and causal_rope_apply of the cache branch (wan/modules/causal_model.py:801-807,
+ * 902-905) on a token slice; the reference has no sequence-parallel form of this path.
+ */
+int sfm_norm_rope_token_slice(const void* q, const void* k, const void* v,
+                              const void* norm_q_weight, const void* norm_k_weight, float eps,
+                              void* q_out, void* k_out, void* v_out, const float* rope,
+                              int B, int n_tokens, int H, int D, int token0, int h, int w,
+                              int start_frame, void* stream);
+
+/*
  * Head-sharded attention across the GPUs of one box (Ulysses style), with the exchange done by
  * the kernels themselves over peer memory instead of two all-to-all collectives.
  *

@@ -34,6 +34,7 @@ SIGNATURES = {
                                   [C.c_int] * 12 + [C.c_void_p]),
     "sfm_rope_cache_write_roll": (C.c_int, [C.c_void_p] * 5 + [C.c_float] + [C.c_void_p] * 3 + [C.c_int64, C.c_void_p] +
                                   [C.c_int] * 14 + [C.c_void_p]),
+    "sfm_norm_rope_token_slice": (C.c_int, [C.c_void_p] * 5 + [C.c_float] + [C.c_void_p] * 4 + [C.c_int] * 8 + [C.c_void_p]),
     "sfm_rope_cache_write_gather": (C.c_int, [C.c_void_p] * 3 + [C.c_int, C.c_int] + [C.c_void_p] * 3 +
                                     [C.c_int64, C.c_void_p] + [C.c_int] * 12 + [C.c_void_p]),
     "sfm_monarch_fwd_scatter": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,

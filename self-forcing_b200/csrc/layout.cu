@@ -37,7 +37,7 @@ rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int
                         int B, int n_new, int H, int start_idx, Blocking blk, int start_frame,
                         int monarch_order, int p0, int p1,
                         const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, float eps,
-                        int roll_dst, int roll_shift) {
+                        int roll_dst, int roll_shift, int rope_tok0) {
     constexpr int kVecPerRow = kHeadDim / 8;  // 16
     __shared__ float2 cs_s[kHeadDim / 2];
     __shared__ float red_s[2][8];
@@ -49,7 +49,8 @@ rope_cache_write_kernel(const __grid_constant__ PeerSrc src, int src_tokens, int
         if (rope) {
             __syncthreads();                                    // previous token's table no longer in use
             for (int m = threadIdx.x; m < kHeadDim / 2; m += blockDim.x) {   // m: rotary pair index within the head
-                const int fr = n / frame_tokens, rem = n - fr * frame_tokens;
+                const int np = n + rope_tok0;                   // position in the chunk's token grid (token slices)
+                const int fr = np / frame_tokens, rem = np - fr * frame_tokens;
                 const int rw = rem / blk.w, cl = rem - rw * blk.w;
                 const int pos = m < p0 ? start_frame + fr : (m < p0 + p1 ? rw : cl);
                 cs_s[m] = rope[pos * (kHeadDim / 2) + m];
@@ -219,7 +220,8 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
                           void* k_cache, void* v_cache, int64_t cache_batch_stride, const float* rope, int B, int n_new,
                           int H, int D, int start_idx, int f_tied, int h_reduce, int w_reduce, int h, int w,
                           int start_frame, int monarch_order, void* stream, const void* wq = nullptr,
-                          const void* wk = nullptr, float eps = 0.f, int roll_dst = 0, int roll_shift = 0) {
+                          const void* wk = nullptr, float eps = 0.f, int roll_dst = 0, int roll_shift = 0,
+                          int rope_tok0 = -1) {
     if (!k_cache || !v_cache) return SFM_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk)) & 15) return SFM_ERR_ALIGNMENT;
     if (have_q && !q_out) return SFM_ERR_NULL_POINTER;
@@ -230,8 +232,11 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
     if (B <= 0 || H <= 0 || n_new <= 0 || start_idx < 0) return SFM_ERR_BAD_SHAPE;
     if (monarch_order && n_new % blk.tied_tokens) return SFM_ERR_BAD_SHAPE;
     if (rope) {
-        if (n_new % (h * w)) return SFM_ERR_BAD_SHAPE;
-        if (start_frame < 0 || start_frame + n_new / (h * w) > 1024 || h > 1024 || w > 1024) return SFM_ERR_BAD_SHAPE;
+        // whole frames, unless the caller rotates a token slice of a chunk (rope_tok0 >= 0: its first token's
+        // index in the chunk's grid)
+        if (rope_tok0 < 0 && n_new % (h * w)) return SFM_ERR_BAD_SHAPE;
+        const int last_frame = start_frame + ((rope_tok0 < 0 ? 0 : rope_tok0) + n_new - 1) / (h * w);
+        if (start_frame < 0 || last_frame >= 1024 || h > 1024 || w > 1024) return SFM_ERR_BAD_SHAPE;
     }
     auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
     if (mis(q_out) || mis(k_cache) || mis(v_cache) || (cache_batch_stride % 8)) return SFM_ERR_ALIGNMENT;
@@ -248,7 +253,7 @@ int rope_cache_write_impl(const PeerSrc& src, bool have_q, int src_tokens, int s
     rope_cache_write_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
         src, src_tokens, src_heads, head0, (uint4*)q_out, (uint4*)k_cache, (uint4*)v_cache, cache_batch_stride / 8,
         (const float2*)rope, B, n_new, H, start_idx, blk, start_frame, monarch_order, p0, p1,
-        (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, eps, roll_dst, roll_shift);
+        (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, eps, roll_dst, roll_shift, rope_tok0 < 0 ? 0 : rope_tok0);
     return (int)cudaGetLastError();
 }
 }  // namespace
@@ -301,6 +306,23 @@ extern "C" int sfm_rope_cache_write_roll(const void* q, const void* k, const voi
     return rope_cache_write_impl(src, true, n_new > 0 ? n_new : 1, H, 0, q_out, k_cache, v_cache, cache_batch_stride,
                                  rope, B, n_new, H, D, start_idx, f_tied, h_reduce, w_reduce, h, w, start_frame,
                                  monarch_order, stream, norm_q_weight, norm_k_weight, eps, roll_dst, roll_shift);
+}
+
+extern "C" int sfm_norm_rope_token_slice(const void* q, const void* k, const void* v, const void* norm_q_weight,
+                                        const void* norm_k_weight, float eps, void* q_out, void* k_out, void* v_out,
+                                        const float* rope, int B, int n_tokens, int H, int D, int token0, int h, int w,
+                                        int start_frame, void* stream) {
+    if (!q || !k || !v || !q_out || !k_out || !v_out || !rope) return SFM_ERR_NULL_POINTER;
+    if ((norm_q_weight == nullptr) != (norm_k_weight == nullptr)) return SFM_ERR_NULL_POINTER;
+    if (!(eps >= 0.f) || token0 < 0) return SFM_ERR_BAD_SHAPE;
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (mis(q) || mis(k) || mis(v)) return SFM_ERR_ALIGNMENT;
+    PeerSrc src = {};
+    src.q[0] = (const uint4*)q; src.k[0] = (const uint4*)k; src.v[0] = (const uint4*)v;
+    // natural order, slot 0 of a "cache" that is just the output tensors
+    return rope_cache_write_impl(src, true, n_tokens > 0 ? n_tokens : 1, H, 0, q_out, k_out, v_out,
+                                 (int64_t)n_tokens * H * D, rope, B, n_tokens, H, D, 0, 1, 1, 1, h, w, start_frame, 0,
+                                 stream, norm_q_weight, norm_k_weight, eps, 0, 0, token0);
 }
 
 extern "C" int sfm_rope_cache_write_gather(const void* const* q_shards, const void* const* k_shards,

@@ -418,17 +418,42 @@ def _ptr_array(ptrs):
     return arr
 
 
+def norm_rope_token_slice(q, k, v, q_out, k_out, v_out, token0, start_frame, h, w, freqs=None, norm_q_weight=None,
+                          norm_k_weight=None, eps=1e-6):
+    """RMSNorm (optional) + RoPE of a token slice of a chunk whose first token is ``token0`` of the chunk's grid:
+    q_out, k_out <- rotated (normalised) q, k; v_out <- v; all [B, n, H, 128] natural order.  One kernel; the
+    outputs may be symmetric-memory buffers that the peers' gather kernels read."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (q_out, "q_out"), (k_out, "k_out"), (v_out, "v_out")):
+        _require(t, name)
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    B, n, H, D = q.shape
+    if any(t.shape != q.shape for t in (k, v, q_out, k_out, v_out)):
+        raise ValueError("all six tensors must share one shape")
+    if (norm_q_weight is None) != (norm_k_weight is None):
+        raise ValueError("give both norm weights or neither")
+    wq = wk = None
+    if norm_q_weight is not None:
+        wq = norm_q_weight.detach().to(device=q.device, dtype=torch.bfloat16).contiguous()
+        wk = norm_k_weight.detach().to(device=q.device, dtype=torch.bfloat16).contiguous()
+    tab = _rope_table_from_freqs(freqs, q.device)
+    rc = _lib.load().sfm_norm_rope_token_slice(_ptr(q), _ptr(k), _ptr(v), _ptr(wq), _ptr(wk), float(eps), _ptr(q_out),
+                                               _ptr(k_out), _ptr(v_out), _ptr(tab), B, n, H, D, int(token0), int(h),
+                                               int(w), int(start_frame), _stream())
+    _lib.check(rc, "sfm_norm_rope_token_slice")
+
+
 def rope_monarch_attn_with_kv_cache_sharded(q_shards, k_shards, v_shards, out_shards, rank, shard_shape, k_cache,
                                             v_cache, start_idx, end_idx, start_frame, f_tied, h_reduce, w_reduce,
-                                            h, w, freqs=None, sm_scale=None):
+                                            h, w, freqs=None, sm_scale=None, rotate=True):
     """Head-sharded form of rope_monarch_attn_with_kv_cache for P GPUs of one box.
 
     ``q_shards[p]``, ``k_shards[p]``, ``v_shards[p]``, ``out_shards[p]`` are device addresses (ints),
     valid on THIS GPU, of GPU p's token shard ``shard_shape = (B, n/P, H_total, 128)`` (bf16,
     contiguous); ``k_cache`` / ``v_cache`` hold this rank's ``H_total/P`` heads.  The gather of the
     inputs and the scatter of the result are done by the kernels over peer memory; the caller
-    puts a barrier before (shards complete) and after (rows landed) the call.  Returns nothing:
-    the result is in the out shards."""
+    puts a barrier before (shards complete) and after (rows landed) the call.  ``rotate=False``: the shards
+    hold q, k that are rotated already (norm_rope_token_slice).  Returns nothing: the result is in the out shards."""
     world = len(q_shards)
     B, sp, h_total, D = shard_shape
     if h_total % world:
@@ -442,7 +467,7 @@ def rope_monarch_attn_with_kv_cache_sharded(q_shards, k_shards, v_shards, out_sh
     if sm_scale is None:
         sm_scale = D ** -0.5
     lib = _lib.load()
-    tab = _rope_table_from_freqs(freqs, k_cache.device)
+    tab = _rope_table_from_freqs(freqs, k_cache.device) if rotate else None     # shards already rotated: gather only
     q_rot = torch.empty((B, n_q, H, D), dtype=torch.bfloat16, device=k_cache.device)
     rc = lib.sfm_rope_cache_write_gather(_ptr_array(q_shards), _ptr_array(k_shards), _ptr_array(v_shards), world,
                                          int(rank), _ptr(q_rot), _ptr(k_cache), _ptr(v_cache), _batch_stride(k_cache),

@@ -105,8 +105,13 @@ class SequenceParallelCausalWan:
         frames, gh, gw = grid
         b, sp = h.shape[:2]
         n, d = attn.num_heads, attn.head_dim
-        q = attn.norm_q(attn.q(h)).view(b, sp, n, d)
-        k = attn.norm_k(attn.k(h)).view(b, sp, n, d)
+        fused = (self.exchange == "peer" and self.world > 1 and h.dtype == torch.bfloat16 and
+                 getattr(attn.norm_q, "weight", None) is not None and attn.norm_q.weight.dtype == torch.bfloat16)
+        if fused:                                  # norms and rotation happen in one kernel further down
+            q, k = attn.q(h).view(b, sp, n, d), attn.k(h).view(b, sp, n, d)
+        else:
+            q = attn.norm_q(attn.q(h)).view(b, sp, n, d)
+            k = attn.norm_k(attn.k(h)).view(b, sp, n, d)
         v = attn.v(h).view(b, sp, n, d)
         n_new = sp * self.world
         step = plan_cache_step(current_start, n_new, cache.global_end, cache.local_end, cache.k.shape[1],
@@ -118,10 +123,17 @@ class SequenceParallelCausalWan:
             if self._peer is None or self._peer.shape != (b, sp, n, d):
                 from .ulysses import PeerShardedSelfAttention
                 self._peer = PeerShardedSelfAttention(self.blocking + (gh, gw), b, n_new, n, h.device, self.group)
-            self._peer.q_in.copy_(q)
-            self._peer.k_in.copy_(k)
-            self._peer.v_in.copy_(v)
-            out = self._peer(cache.k, cache.v, step.local_start, step.local_end, start_frame)
+            if fused:
+                from . import ops
+                # RMSNorm + RoPE of this rank's token slice, written straight into the buffers the peers read
+                ops.norm_rope_token_slice(q, k, v, self._peer.q_in, self._peer.k_in, self._peer.v_in, self.rank * sp,
+                                          start_frame, gh, gw, freqs=self.model.freqs, norm_q_weight=attn.norm_q.weight,
+                                          norm_k_weight=attn.norm_k.weight, eps=attn.eps)
+            else:
+                self._peer.q_in.copy_(q)
+                self._peer.k_in.copy_(k)
+                self._peer.v_in.copy_(v)
+            out = self._peer(cache.k, cache.v, step.local_start, step.local_end, start_frame, rotate=not fused)
         else:
             if self._ulysses is None:
                 self._ulysses = UlyssesSelfAttention(self.blocking + (gh, gw), self.group, self.attn_fn, self.num_iters)

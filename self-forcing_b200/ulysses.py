@@ -135,11 +135,12 @@ class PeerShardedSelfAttention:
     def barrier(self):
         self._hdl.barrier()
 
-    def __call__(self, k_cache, v_cache, start_idx, end_idx, start_frame=0):
+    def __call__(self, k_cache, v_cache, start_idx, end_idx, start_frame=0, rotate=True):
+        """``rotate=False`` when q_in / k_in already hold rotated values (ops.norm_rope_token_slice)."""
         from . import ops
         self._hdl.barrier()                       # every rank's q_in / k_in / v_in are complete
         ops.rope_monarch_attn_with_kv_cache_sharded(self._ptrs[0], self._ptrs[1], self._ptrs[2], self._ptrs[3],
                                                     self.rank, self.shape, k_cache, v_cache, start_idx, end_idx,
-                                                    start_frame, *self.blocking)
+                                                    start_frame, *self.blocking, rotate=rotate)
         self._hdl.barrier()                       # every rank's rows have landed in self.out
         return self.out

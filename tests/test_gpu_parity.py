@@ -666,3 +666,29 @@ def test_dense_status_word_is_read_and_cleared(sfb):
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     assert lib.sfm_dense_status(stream) == 0
     ops.check_device_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("parts", [2, 8])
+def test_norm_rope_token_slices_equal_the_whole_chunk(sfb, parts):
+    """Sequence-parallel front end: RMSNorm + RoPE applied slice by slice (each slice knowing its first token's
+    position in the chunk's grid) equals the one-pass kernel on the whole chunk bit for bit, with slices that cut
+    through frames and rows."""
+    from self_forcing_b200 import ops
+    rng = np.random.default_rng(12)
+    B, H, gh, gw = 2, 3, 6, 8
+    n = 3 * gh * gw                                            # 144 tokens: 72 / 18 per slice
+    q, k, v = (bf(cases.randn(rng, B, n, H, 128)).cuda() for _ in range(3))
+    wq = bf(torch.from_numpy(rng.uniform(0.7, 1.3, size=H * 128).astype(np.float32))).cuda()
+    wk = bf(torch.from_numpy(rng.uniform(0.7, 1.3, size=H * 128).astype(np.float32))).cuda()
+    kc, vc = torch.zeros_like(k), torch.zeros_like(v)
+    q_ref = ops.norm_rope_cache_write(q, k, v, kc, vc, 0, 5, 1, 1, 1, gh, gw, norm_q_weight=wq, norm_k_weight=wk,
+                                      monarch_order=False)
+    sp = n // parts
+    for r in range(parts):
+        sl = slice(r * sp, (r + 1) * sp)
+        qo, ko, vo = (torch.empty(B, sp, H, 128, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+        ops.norm_rope_token_slice(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous(), qo, ko, vo,
+                                  r * sp, 5, gh, gw, norm_q_weight=wq, norm_k_weight=wk)
+        torch.cuda.synchronize()
+        assert torch.equal(qo, q_ref[:, sl]) and torch.equal(ko, kc[:, sl]) and torch.equal(vo, vc[:, sl])
