@@ -10,7 +10,10 @@ using namespace sfm;
 namespace sfm {
 int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps, int rows_per_group, int n_s, int* status,
                      int num_sms, cudaStream_t s);
-int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps, int* status, int num_sms, cudaStream_t s);
+int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps, int* status, int num_sms, cudaStream_t s,
+                     int write_lse = 0);
+int launch_l_iter_tc(const MonarchParams& p, const CUtensorMap* map_al, const CUtensorMap* map_qrows, int* status,
+                     int num_sms, cudaStream_t s);
 }
 
 namespace {
@@ -134,9 +137,10 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
     p.scale = sm_scale;
     p.blk = pl.blk;
 
-    // Tensor-core path: single pass (block-causal included, for block rows up to 128).  The iterative
-    // variant runs on the mma.sync kernels.
-    const bool use_tc = num_iters == 1 && (causal_groups == 0 || pl.blk.b1 <= 128);
+    // Tensor-core path: single pass (block-causal included, for block rows up to 128) and the iterative variant
+    // for block rows up to 128 and block columns up to 64; everything else runs on the mma.sync kernels.
+    const bool iter_tc = num_iters > 1 && pl.blk.b1 <= 128 && pl.blk.b2 <= kB2Max;
+    const bool use_tc = (num_iters == 1 && (causal_groups == 0 || pl.blk.b1 <= 128)) || iter_tc;
     // block columns above 64 exist on the tensor-core kernels only (single pass, block rows up to 128)
     if (pl.blk.b2 > kB2Max && !(use_tc && pl.blk.b1 <= 128)) return SFM_ERR_UNSUPPORTED;
     // only the tensor-core column step knows how to scatter its rows
@@ -147,7 +151,7 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
     int* status = reinterpret_cast<int*>(base + pl.off_status);
-    CUtensorMap maps[6];
+    CUtensorMap maps[7];
     const int rows_per_group = (pl.blk.b2 + 7) & ~7;
     const int n_s = (pl.blk.b2 + 15) & ~15;
     {
@@ -225,6 +229,15 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
             }
             p.f_per = (pl.F + fsplit - 1) / fsplit;
             p.fsplit = (pl.F + p.f_per - 1) / p.f_per;
+            if (iter_tc) {
+                // iteration state aR of this chunk as [nbh * F * b1][na * b2][128]: one (f, k) block of stacked
+                // (query group, column) rows per index of the slowest dimension
+                const uint64_t row = (uint64_t)kHeadDim * 2;
+                uint64_t dar[3] = {(uint64_t)kHeadDim, (uint64_t)p.na * pl.blk.b2, (uint64_t)p.nbh * pl.F * pl.blk.b1};
+                uint64_t sar[2] = {row, (uint64_t)p.na * pl.blk.b2 * row};
+                uint32_t bar[3] = {64, (uint32_t)rows_per_group, 1};
+                if ((rc = make_tmap_bf16(&maps[6], p.aR, 3, dar, sar, bar))) return rc;
+            }
 
             for (int it = 0; it < num_iters; ++it) {
                 const bool last = it == num_iters - 1;
@@ -232,7 +245,9 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                 p.write_Y = last;
                 p.mult0 = num_iters > 1 ? sm_scale * (1.0f / (1.0f + 1e-6f)) : sm_scale;
                 if (use_tc) {
-                    if ((rc = launch_r_step_tc(p, maps, rows_per_group, n_s, status, num_sms, stream))) return rc;
+                    // later passes of the iterative variant read their query operand from the state aR
+                    CUtensorMap rmaps[3] = {p.use_aR ? maps[6] : maps[0], maps[1], maps[2]};
+                    if ((rc = launch_r_step_tc(p, rmaps, rows_per_group, n_s, status, num_sms, stream))) return rc;
                 } else {
                     if ((rc = launch_r_step(p, stream))) return rc;
                 }
@@ -240,6 +255,11 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                     if (use_tc && pl.blk.b1 <= 128) {
                         if ((rc = launch_l_step_tc(p, maps + 3, status, num_sms, stream))) return rc;
                     } else if ((rc = launch_l_step(p, 0, stream))) return rc;
+                } else if (iter_tc) {
+                    // the column step's softmax statistics (its output row is overwritten by the last pass), then
+                    // the update of the state
+                    if ((rc = launch_l_step_tc(p, maps + 3, status, num_sms, stream, 1))) return rc;
+                    if ((rc = launch_l_iter_tc(p, &maps[3], &maps[5], status, num_sms, stream))) return rc;
                 } else {
                     if ((rc = launch_l_step(p, 1, stream))) return rc;
                     if ((rc = launch_l_iter(p, stream))) return rc;

@@ -52,6 +52,7 @@ struct LTcParams {
     int q_rows_tma;  // the query rows of a unit are consecutive rows of the token grid: load them with TMA
     int n_kv;        // dense: keys per (batch, head)
     int q_tiles;     // dense: ceil(n_q / 128)
+    int write_lse;   // column step: also store the log-sum-exp of every query row (iterative variant)
     int* status;
 };
 
@@ -555,6 +556,8 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
                     const long long tok = blk.row_token(p.a0 + un.al, i_row) + un.j;
                     out_row = p.out_row(b, tok, hd);
+                    // iterative variant: the softmax's log-sum-exp (natural log) feeds the iteration update
+                    if (lp.write_lse) p.lse[(long long)(u0 + us) * b1 + i_row] = (ms + log2f(w0 * l0 + w1 * l1)) * 0.6931471805599453f;
                 }
             }
 #pragma unroll 1
@@ -596,7 +599,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
 // Launches the tensor-core column step for one chunk as a persistent grid.  maps = {aL, Y} with a
 // (64, 128 keys, 1) box and the 5-D query-row map (box rows = ceil(b1/4)).
 int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q rows */, int* status, int num_sms,
-                     cudaStream_t s) {
+                     cudaStream_t s, int write_lse) {
     LaunchScope scope(kClsLStep, s);
     LTcParams lp;
     lp.mp = p;
@@ -612,6 +615,7 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
     lp.q_rows_tma = (p.blk.f_tied == 1 || p.blk.h_reduce == 1) ? 1 : 0;
     lp.n_kv = 0;
     lp.q_tiles = 0;
+    lp.write_lse = write_lse;
     const int n_groups = (lp.n_units + lp.U - 1) / lp.U;
     dim3 grid(n_groups < num_sms ? n_groups : num_sms);
     auto kernel = p.causal_groups > 0 ? monarch_l_tc_kernel<false, true> : monarch_l_tc_kernel<false, false>;
@@ -639,6 +643,7 @@ int launch_dense_tc(const CUtensorMap* maps, __nv_bfloat16* out, int B, int H, i
     lp.R4 = 32;
     lp.n_kv = n_kv;
     lp.q_rows_tma = 1;
+    lp.write_lse = 0;
     lp.status = status;
     dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
     cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

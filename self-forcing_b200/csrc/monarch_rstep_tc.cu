@@ -76,7 +76,7 @@ __device__ __forceinline__ RUnit decode_unit(const RTcParams& rp, int u) {
 }
 
 struct __align__(8) Barriers {
-    uint64_t q_full, q_empty;
+    uint64_t q_full[2], q_empty[2];   // single pass: buffer 0, once per unit; iterative variant: one per step, alternating
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
     uint64_t s_full[2];
@@ -99,15 +99,20 @@ __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) 
                  "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 
-template <int N_S, bool kCausal>
+// kIter: a pass of the iterative variant after the first one.  The query operand is no longer the chunk's q
+// (one tile per unit) but the state aR[a,f,k,j,:] of the previous pass, which differs for every cached group f:
+// one tile per STEP, loaded through `tq` = a 3-D map of aR ([bh*F*b1][na*b2][128]) into two alternating
+// buffers, and every row's logits are divided by its cR (monarch_attn.py:1716-1719).
+template <int N_S, bool kCausal, bool kIter>
 __global__ void __launch_bounds__(kThreads, 1)
 monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, RTcParams rp) {
+    static_assert(!kIter || (N_S <= 64 && !kCausal), "the iterative variant exists for block columns up to 64, no mask");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
-    unsigned char* kv_s = q_s + kQBytes;
-    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + (N_S > 64 ? 2 * 2 * kStageBytes : kStages * kStageBytes));
+    unsigned char* kv_s = q_s + (kIter ? 2 : 1) * kQBytes;
+    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + (N_S > 64 ? 2 * 2 * kStageBytes : (kIter ? kStages - 1 : kStages) * kStageBytes));
 
     const MonarchParams& p = rp.mp;
     const Blocking& blk = p.blk;
@@ -118,13 +123,12 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     // Block columns above 64 (wide grids): 128-row K / V stages (two of them fit), S/P buffers and the
     // accumulator move up in TMEM, and the softmax walks its row in 32-column chunks (see below).
     constexpr bool kWide = N_S > 64;
-    constexpr int kStg = kWide ? 2 : kStages;
+    constexpr int kStg = kWide ? 2 : (kIter ? kStages - 1 : kStages);
     constexpr int kStgBytes = kWide ? 2 * kStageBytes : kStageBytes;
     constexpr uint32_t cS1 = kWide ? 128u : kColS1, cO = kWide ? 256u : kColO;
 
     if (tid == 0) {
-        mbar_init(&bars->q_full, 1);
-        mbar_init(&bars->q_empty, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); }
         for (int s = 0; s < kStg; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->s_full[s], 1); mbar_init(&bars->p_full[s], 128); }
         for (int s = 0; s < 2; ++s) mbar_init(&bars->sp_free[s], 1);
@@ -156,15 +160,29 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
                 const int g_first = un.tile * rp.groups_per_tile;
                 const int ng = min(rp.groups_per_tile, p.na - g_first);
-                if (uc > 0 && !mbar_wait(&bars->q_empty, (uc - 1) & 1)) { fail(10); break; }
-                mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ng * RG * 256));
-                for (int gi = 0; gi < ng; ++gi) {
-                    int tok = blk.row_token(p.a0 + g_first + gi, un.k);
-                    tma_load_4d(q_s + gi * RG * 128, &tq, &bars->q_full, 0, hd, tok, b);
-                    tma_load_4d(q_s + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full, 64, hd, tok, b);
+                if constexpr (!kIter) {
+                    if (uc > 0 && !mbar_wait(&bars->q_empty[0], (uc - 1) & 1)) { fail(10); break; }
+                    mbar_arrive_expect_tx(&bars->q_full[0], (uint32_t)(ng * RG * 256));
+                    for (int gi = 0; gi < ng; ++gi) {
+                        int tok = blk.row_token(p.a0 + g_first + gi, un.k);
+                        tma_load_4d(q_s + gi * RG * 128, &tq, &bars->q_full[0], 0, hd, tok, b);
+                        tma_load_4d(q_s + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full[0], 64, hd, tok, b);
+                    }
                 }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStg;
+                    if constexpr (kIter) {
+                        // this step's query tile: the state rows (a, j) of (f, k), group by group
+                        const int qb = g & 1;
+                        if (g >= 2 && !mbar_wait(&bars->q_empty[qb], ((g >> 1) - 1) & 1)) { fail(10); break; }
+                        unsigned char* qd = q_s + qb * kQBytes;
+                        const int fk = (un.bhl * p.F + un.f_begin + i) * b1 + un.k;
+                        mbar_arrive_expect_tx(&bars->q_full[qb], (uint32_t)(ng * RG * 256));
+                        for (int gi = 0; gi < ng; ++gi) {
+                            tma_load_3d(qd + gi * RG * 128, &tq, &bars->q_full[qb], 0, (g_first + gi) * b2, fk);
+                            tma_load_3d(qd + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full[qb], 64, (g_first + gi) * b2, fk);
+                        }
+                    }
                     if (g >= kStg && !mbar_wait(&bars->kv_empty[s], ((g / kStg) - 1) & 1)) { fail(11); break; }
                     const int tok = ((un.f_begin + i) * b1 + un.k) * b2;
                     unsigned char* st = kv_s + s * kStgBytes;
@@ -190,9 +208,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             for (int u = u_first; ok && u < rp.n_units && !bars->abort_flag; u += u_stride) {
                 const RUnit un = decode_unit<kCausal>(rp, u);
                 if (kCausal && un.n_it == 0) continue;
-                if (!mbar_wait(&bars->q_full, uc & 1)) { fail(20); break; }
+                if constexpr (!kIter) {
+                    if (!mbar_wait(&bars->q_full[0], uc & 1)) { fail(20); break; }
+                }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStg;
+                    if constexpr (kIter) {
+                        if (!mbar_wait(&bars->q_full[g & 1], (g >> 1) & 1)) { fail(20); ok = false; break; }
+                    }
                     if (!mbar_wait(&bars->kv_full[s], (g / kStg) & 1)) { fail(21); ok = false; break; }
                     if (g >= 2 && !mbar_wait(&bars->sp_free[g & 1], ((g >> 1) - 1) & 1)) { fail(25); ok = false; break; }
                     tc_fence_after();
@@ -202,10 +225,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     for (int ks = 0; ks < 8; ++ks) {
                         const uint32_t q_off = ((ks >> 2) * (kTileRows * 128) + (ks & 3) * 32) >> 4;
                         const uint32_t k_off = ((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-                        mma_ss(d, q_desc + q_off, kd + k_off, idesc_s, ks > 0);
+                        mma_ss(d, q_desc + (kIter ? (uint32_t)(((g & 1) * kQBytes) >> 4) : 0u) + q_off, kd + k_off, idesc_s, ks > 0);
                     }
                     mma_commit(&bars->s_full[g & 1]);
-                    if (i + 1 == un.n_it) mma_commit(&bars->q_empty);   // last read of this unit's Q tile
+                    if constexpr (kIter) {
+                        mma_commit(&bars->q_empty[g & 1]);                 // this step's query tile has been read
+                    } else {
+                        if (i + 1 == un.n_it) mma_commit(&bars->q_empty[0]);   // last read of this unit's Q tile
+                    }
                 }
                 ++uc;
             }
@@ -257,6 +284,15 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             const int f_allowed = kCausal ? ((p.a0 + g_first + gl) / p.causal_groups + 1) * p.causal_groups : p.F;
             for (int i = 0; i < un.n_it; ++i, ++g) {
                 if ((g & 1) != wg) continue;
+                float scale_row = scale_l2;
+                if constexpr (kIter) {
+                    // logits are divided by the row's cR of the previous pass (clamped as in the reference)
+                    if (row_ok) {
+                        const long long ci = (((long long)un.bhl * p.F + un.f_begin + i) * b1 + un.k) * (long long)(p.na * b2) +
+                                             (long long)(g_first + gl) * b2 + j;
+                        scale_row = p.scale * kLog2e * fminf(1.0f / (p.cR[ci] + 1e-6f), 1e4f);
+                    }
+                }
                 if (!mbar_wait(&bars->s_full[wg], (g >> 1) & 1)) { fail(31); ok = false; break; }
                 tc_fence_after();
                 if (warp_active) {
@@ -281,9 +317,9 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     float mx = -INFINITY;
 #pragma unroll
                     for (int c = 0; c < N_S; c += 2) mx = max3(mx, __uint_as_float(raw[c]), __uint_as_float(raw[c + 1]));
-                    const float neg_m = -mx * scale_l2;
+                    const float neg_m = -mx * scale_row;
                     // two columns at a time on the packed fp32 pipe
-                    const uint64_t scale2 = f2_pack(scale_l2, scale_l2), negm2 = f2_pack(neg_m, neg_m);
+                    const uint64_t scale2 = f2_pack(scale_row, scale_row), negm2 = f2_pack(neg_m, neg_m);
                     uint64_t z2 = f2_pack(0.f, 0.f), ent2 = z2;
                     uint64_t e2[N_S / 2];
 #pragma unroll
@@ -465,8 +501,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 
 // Launches the tensor-core row step for one chunk as a persistent grid.  `status` is a device int the
 // kernel sets on an internal timeout.
-int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v */, int rows_per_group, int n_s,
-                     int* status, int num_sms, cudaStream_t s) {
+int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q (or the aR state), k, v */, int rows_per_group,
+                     int n_s, int* status, int num_sms, cudaStream_t s) {
     LaunchScope scope(kClsRStep, s);
     RTcParams rp;
     rp.mp = p;
@@ -477,7 +513,10 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v 
     rp.status = status;
     dim3 grid(rp.n_units < num_sms ? rp.n_units : num_sms);
     // wide blocks: two 64 KB K / V stages instead of five 32 KB ones
-    const int smem_bytes = n_s > 64 ? 1024 + kQBytes + 2 * 2 * kStageBytes + 256 : kSmemBytes;
+    const bool iter = p.use_aR != 0;
+    if (iter && (n_s > 64 || p.causal_groups > 0)) return SFM_ERR_UNSUPPORTED;
+    const int smem_bytes = n_s > 64 ? 1024 + kQBytes + 2 * 2 * kStageBytes + 256
+                                    : (iter ? 1024 + 2 * kQBytes + (kStages - 1) * kStageBytes + 256 : kSmemBytes);
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return (int)e;
@@ -486,15 +525,23 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q, k, v 
     };
     int rc;
     const bool causal = p.causal_groups > 0;
-    switch (n_s) {
-        case 16: rc = causal ? go(monarch_r_tc_kernel<16, true>) : go(monarch_r_tc_kernel<16, false>); break;
-        case 32: rc = causal ? go(monarch_r_tc_kernel<32, true>) : go(monarch_r_tc_kernel<32, false>); break;
-        case 48: rc = causal ? go(monarch_r_tc_kernel<48, true>) : go(monarch_r_tc_kernel<48, false>); break;
-        case 64: rc = causal ? go(monarch_r_tc_kernel<64, true>) : go(monarch_r_tc_kernel<64, false>); break;
-        case 80: rc = causal ? go(monarch_r_tc_kernel<80, true>) : go(monarch_r_tc_kernel<80, false>); break;
-        case 96: rc = causal ? go(monarch_r_tc_kernel<96, true>) : go(monarch_r_tc_kernel<96, false>); break;
-        case 112: rc = causal ? go(monarch_r_tc_kernel<112, true>) : go(monarch_r_tc_kernel<112, false>); break;
-        case 128: rc = causal ? go(monarch_r_tc_kernel<128, true>) : go(monarch_r_tc_kernel<128, false>); break;
+    if (iter) {
+        switch (n_s) {
+            case 16: rc = go(monarch_r_tc_kernel<16, false, true>); break;
+            case 32: rc = go(monarch_r_tc_kernel<32, false, true>); break;
+            case 48: rc = go(monarch_r_tc_kernel<48, false, true>); break;
+            case 64: rc = go(monarch_r_tc_kernel<64, false, true>); break;
+            default: return SFM_ERR_UNSUPPORTED;
+        }
+    } else switch (n_s) {
+        case 16: rc = causal ? go(monarch_r_tc_kernel<16, true, false>) : go(monarch_r_tc_kernel<16, false, false>); break;
+        case 32: rc = causal ? go(monarch_r_tc_kernel<32, true, false>) : go(monarch_r_tc_kernel<32, false, false>); break;
+        case 48: rc = causal ? go(monarch_r_tc_kernel<48, true, false>) : go(monarch_r_tc_kernel<48, false, false>); break;
+        case 64: rc = causal ? go(monarch_r_tc_kernel<64, true, false>) : go(monarch_r_tc_kernel<64, false, false>); break;
+        case 80: rc = causal ? go(monarch_r_tc_kernel<80, true, false>) : go(monarch_r_tc_kernel<80, false, false>); break;
+        case 96: rc = causal ? go(monarch_r_tc_kernel<96, true, false>) : go(monarch_r_tc_kernel<96, false, false>); break;
+        case 112: rc = causal ? go(monarch_r_tc_kernel<112, true, false>) : go(monarch_r_tc_kernel<112, false, false>); break;
+        case 128: rc = causal ? go(monarch_r_tc_kernel<128, true, false>) : go(monarch_r_tc_kernel<128, false, false>); break;
         default: return SFM_ERR_UNSUPPORTED;
     }
     if (rc) return rc;
