@@ -272,6 +272,87 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
 
 }  // namespace
 
+namespace sfm {
+// Single-pass forward on the tensor-core kernels for the (batch, head) pairs [bh0, bh0 + nbh) with all query
+// groups at once, into caller-given bridge buffers (aL, Y: bf16 [slab][n_keys][128], cL: fp32 [slab][n_keys_c],
+// slab = (bh_local * A + a) * b2 + j) and, optionally, the column step's log-sum-exp per query row
+// (lse: fp32 [slab][b1]).  The backward uses it to recompute what the forward did not keep.  Returns the launch
+// parameters and the six tensor maps (q, K, V, aL bridge, Y bridge, query rows) for the kernels that follow.
+int forward_tc_slice(const void* q, int64_t q_bs, const void* kc, const void* vc, int64_t c_bs, void* out,
+                     __nv_bfloat16* aL, __nv_bfloat16* Y, float* cL, float* lse, int* status, int B, int H, int n_q,
+                     int n_kv, const Blocking& blk, float scale, int bh0, int nbh, MonarchParams* p_out,
+                     CUtensorMap* maps, cudaStream_t stream) {
+    if (blk.b1 > 128 || blk.b2 > kB2MaxTc) return SFM_ERR_UNSUPPORTED;
+    const int group = blk.b1 * blk.b2;
+    MonarchParams p;
+    p.q = (const __nv_bfloat16*)q; p.q_bs = q_bs;
+    p.kc = (const __nv_bfloat16*)kc; p.vc = (const __nv_bfloat16*)vc; p.c_bs = c_bs;
+    p.out = (__nv_bfloat16*)out;
+    for (int i = 0; i < kMaxPeers; ++i) p.out_peers[i] = nullptr;
+    p.out_peers[0] = (__nv_bfloat16*)out;
+    p.out_tokens = n_q; p.out_heads = H; p.out_head0 = 0;
+    p.aL = aL; p.Y = Y; p.cL = cL; p.lse = lse; p.aR = nullptr; p.cR = nullptr;
+    p.H = H; p.n_q = n_q; p.A = n_q / group; p.F = n_kv / group; p.n_keys = p.F * blk.b1;
+    p.n_keys_c = (p.n_keys + 3) & ~3;
+    p.na_cta = std::max(1, std::min(p.A, kRMaxRows / blk.b2));
+    p.causal_groups = 0;
+    p.scale = scale; p.mult0 = scale;
+    p.blk = blk;
+    p.bh0 = bh0; p.nbh = nbh; p.a0 = 0; p.na = p.A;
+    p.use_aR = 0; p.write_Y = 1;
+    int num_sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int rows_per_group = (blk.b2 + 7) & ~7;
+    const int n_s = (blk.b2 + 15) & ~15;
+    const size_t slabs = (size_t)nbh * p.A * blk.b2;
+    cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(cL, 0x7f, slabs * p.n_keys_c * sizeof(float), stream);
+    if (e != cudaSuccess) return (int)e;
+    int rc;
+    const uint64_t row = (uint64_t)kHeadDim * 2, tok = (uint64_t)H * row;
+    uint64_t dq[4] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)n_q, (uint64_t)B};
+    uint64_t sq[3] = {row, tok, (uint64_t)q_bs * 2};
+    uint32_t bq[4] = {64, 1, (uint32_t)rows_per_group, 1};
+    uint64_t dk[4] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)n_kv, (uint64_t)B};
+    uint64_t sk[3] = {row, tok, (uint64_t)c_bs * 2};
+    uint32_t bk[4] = {64, 1, (uint32_t)n_s, 1};
+    uint64_t db[3] = {(uint64_t)kHeadDim, (uint64_t)p.n_keys, (uint64_t)slabs};
+    uint64_t sb[2] = {row, (uint64_t)p.n_keys * row};
+    uint32_t bb[3] = {64, 128, 1};
+    const int rows_per_quadrant = (blk.b1 + 3) / 4;
+    uint64_t dqr[5] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)blk.w, (uint64_t)(n_q / blk.w), (uint64_t)B};
+    uint64_t sqr[4] = {row, tok, (uint64_t)blk.w * tok, (uint64_t)q_bs * 2};
+    uint32_t bqr[5] = {64, 1, 1, (uint32_t)rows_per_quadrant, 1};
+    if ((rc = make_tmap_bf16(&maps[0], q, 4, dq, sq, bq))) return rc;
+    if ((rc = make_tmap_bf16(&maps[1], kc, 4, dk, sk, bk))) return rc;
+    if ((rc = make_tmap_bf16(&maps[2], vc, 4, dk, sk, bk))) return rc;
+    if ((rc = make_tmap_bf16(&maps[3], aL, 3, db, sb, bb))) return rc;
+    if ((rc = make_tmap_bf16(&maps[4], Y, 3, db, sb, bb))) return rc;
+    if ((rc = make_tmap_bf16(&maps[5], q, 5, dqr, sqr, bqr))) return rc;
+    // split of the F loop over persistent CTAs, as in the forward proper
+    const int asubs = (p.na + (128 / rows_per_group) - 1) / (128 / rows_per_group);
+    const int base_ctas = blk.b1 * asubs * nbh;
+    int fsplit = 1;
+    long long best = -1;
+    for (int fs = 1; fs <= std::max(1, p.F / 3); ++fs) {
+        const int per = (p.F + fs - 1) / fs;
+        const int splits = (p.F + per - 1) / per;
+        const long long units = (long long)base_ctas * splits;
+        const long long cost = ((units + num_sms - 1) / num_sms) * (per + 1);
+        if (best < 0 || cost < best) { best = cost; fsplit = fs; }
+    }
+    p.f_per = (p.F + fsplit - 1) / fsplit;
+    p.fsplit = (p.F + p.f_per - 1) / p.f_per;
+    if ((rc = launch_r_step_tc(p, maps, rows_per_group, n_s, status, num_sms, stream))) return rc;
+    if ((rc = launch_l_step_tc(p, maps + 3, status, num_sms, stream, lse ? 1 : 0))) return rc;
+    *p_out = p;
+    return SFM_OK;
+}
+}  // namespace sfm
+
 extern "C" int sfm_version(void) { return 100; }
 
 // Reads (and thereby waits for) the status word the kernels of the last call on `workspace` left.

@@ -26,11 +26,20 @@
 // (dK / dV only for a range of cached groups).  Unlike that code it accumulates dQ without atomics and keeps
 // the intermediate gradients in fp32.
 #include <algorithm>
+#include <cstdlib>
 
-#include "common.cuh"
+#include "monarch_params.cuh"
 #include "profile.cuh"
+#include "tc05.cuh"
 
 namespace sfm {
+int forward_tc_slice(const void* q, int64_t q_bs, const void* kc, const void* vc, int64_t c_bs, void* out,
+                     __nv_bfloat16* aL, __nv_bfloat16* Y, float* cL, float* lse, int* status, int B, int H, int n_q,
+                     int n_kv, const Blocking& blk, float scale, int bh0, int nbh, MonarchParams* p_out,
+                     CUtensorMap* maps, cudaStream_t stream);
+int launch_bwd_delta(const void* dout, const void* out, float* delta, long long rows, cudaStream_t s);
+int launch_bwd_col_tc(const MonarchParams& mp, const CUtensorMap* maps, const float* delta, float* dcL, float* dq,
+                      int* status, int num_sms, cudaStream_t s);
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -50,6 +59,8 @@ struct BwdParams {
     float* dq2;                    // scratch like dq: the share of the second half of the cached groups (row kernel)
     bf16 *dk, *dv;
     float *aL, *Y, *cL, *dcL;      // scratch; aL / Y hold daL / dY after the column kernel
+    const bf16 *aLb, *Yb;          // tensor-core path: daL / dY as bf16 (gradients of the UNSCALED aL), else null
+    int dcl_pitch;                 // row pitch of dcL in floats
     int64_t q_bs, kv_bs;           // batch strides of q and of the cache, in elements
     int H, A, F, b1, b2, n_keys, n_q;
     int bh0;                       // first (batch, head) pair of this slice
@@ -466,9 +477,19 @@ __global__ void __launch_bounds__(512) bwd_row_kernel(const BwdParams p) {
                     // a pair (a, f) the query group may not see has zero gradients (its scratch rows still hold forward values)
                     const bool seen = f < p.groups_seen(a);
                     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    const float4 a4 = seen ? *reinterpret_cast<const float4*>(p.aL + o + lane * 4) : zero4;
-                    const float4 y4 = seen ? *reinterpret_cast<const float4*>(p.Y + o + lane * 4) : zero4;
-                    dcl[e] = seen ? p.dcL[slab * p.n_keys + n] : 0.f;
+                    float4 a4 = zero4, y4 = zero4;
+                    if (seen) {
+                        if (p.aLb) {            // bf16 gradients of the unscaled aL: daL of the scaled one = that / sqrt(scale)
+                            const float4 t4 = ld4(p.aLb + o + lane * 4);
+                            const float ir = 1.0f / p.rs;
+                            a4 = make_float4(t4.x * ir, t4.y * ir, t4.z * ir, t4.w * ir);
+                            y4 = ld4(p.Yb + o + lane * 4);
+                        } else {
+                            a4 = *reinterpret_cast<const float4*>(p.aL + o + lane * 4);
+                            y4 = *reinterpret_cast<const float4*>(p.Y + o + lane * 4);
+                        }
+                    }
+                    dcl[e] = seen ? p.dcL[slab * p.dcl_pitch + n] : 0.f;
                     *reinterpret_cast<float4*>(qS + slot * kD + lane * 4) =
                         make_float4(q4.x * p.rs, q4.y * p.rs, q4.z * p.rs, q4.w * p.rs);
                     *reinterpret_cast<float4*>(daS + slot * kD + lane * 4) = a4;
@@ -681,6 +702,9 @@ int make_bwd_plan(BwdPlan* pl, int B, int H, int D, int n_q, int n_kv, int f_tie
     pl->off_cL = o; o = up256(o + units * sizeof(float));
     pl->off_dcL = o; o = up256(o + units * sizeof(float));
     pl->off_dq2 = o; o = up256(o + (size_t)B * n_q * H * kHeadDim * sizeof(float));
+    // the tensor-core path lays the same region out differently (bf16 bridge, log-sum-exp, a scratch output,
+    // delta, a status word) and never needs more than this
+    o += up256((size_t)B * n_q * H * (kHeadDim * 2 + 4)) + up256((size_t)pl->nbh * pl->A * blk.b2 * (blk.b1 + 8) * sizeof(float)) + 4096;
     pl->total = o;
     return SFM_OK;
 }
@@ -733,6 +757,14 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     p.causal_groups = causal_groups;
     p.scale = sm_scale; p.rs = sqrtf(sm_scale);
     p.blk = blk;
+    p.aLb = p.Yb = nullptr;
+    p.dcl_pitch = pl.n_keys;
+    // Tensor-core path: recompute of the forward's row step (and of the column step, for its softmax statistics
+    // and output) on the forward's own tcgen05 kernels, column-step backward on tcgen05; block rows up to 32,
+    // query rows reachable by TMA, no block-causal mask.  SFM_BWD_FP32=1 keeps everything on the fp32 kernels.
+    const char* force_fp32 = getenv("SFM_BWD_FP32");
+    const bool use_tc = causal_groups == 0 && blk.b1 <= 32 && blk.b2 <= 64 && (blk.f_tied == 1 || blk.h_reduce == 1) &&
+                        !(force_fp32 && force_fp32[0] == '1');
 
     const int T = blk.b1 <= 16 ? 2 : (blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16));
     const int LT = blk.b2 <= 64 ? 16 : 32;
@@ -749,9 +781,50 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
 
     cudaStream_t s = (cudaStream_t)stream;
     const int BH = B * H;
+    int num_sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
     for (int bh0 = 0; bh0 < BH; bh0 += pl.nbh) {
         const int nbh = std::min(pl.nbh, BH - bh0);
         p.bh0 = bh0;
+        if (use_tc) {
+            // workspace of this slice: status | aL, Y (bf16 bridge) | cL, dcL | lse | out (scratch) | delta | dq2
+            const size_t slabs = (size_t)nbh * pl.A * blk.b2;
+            const int n_keys_c = (pl.n_keys + 3) & ~3;
+            const size_t rows = (size_t)B * n_q * H;
+            size_t o = 0;
+            int* status = (int*)(ws + o); o = up256(o + sizeof(int));
+            bf16* aLb = (bf16*)(ws + o); o = up256(o + slabs * pl.n_keys * kHeadDim * sizeof(bf16));
+            bf16* Yb = (bf16*)(ws + o); o = up256(o + slabs * pl.n_keys * kHeadDim * sizeof(bf16));
+            float* cL = (float*)(ws + o); o = up256(o + slabs * n_keys_c * sizeof(float));
+            float* dcL = (float*)(ws + o); o = up256(o + slabs * n_keys_c * sizeof(float));
+            float* lse = (float*)(ws + o); o = up256(o + slabs * blk.b1 * sizeof(float));
+            bf16* out_s = (bf16*)(ws + o); o = up256(o + rows * kHeadDim * sizeof(bf16));
+            float* delta = (float*)(ws + o); o = up256(o + rows * sizeof(float));
+            p.dq2 = (float*)(ws + o); o = up256(o + rows * kHeadDim * sizeof(float));
+            if (o > workspace_bytes) return SFM_ERR_WORKSPACE;
+            MonarchParams mp;
+            CUtensorMap maps[8];
+            int rc = forward_tc_slice(q, q_batch_stride, k_cache, v_cache, kv_batch_stride, out_s, aLb, Yb, cL, lse, status,
+                                      B, H, n_q, n_kv, blk, sm_scale, bh0, nbh, &mp, maps, s);
+            if (rc) return rc;
+            // delta = dOut . out for every (token, head); the scratch output holds this slice's heads only, the
+            // other heads' products are never read
+            if ((rc = launch_bwd_delta(dout, out_s, delta, (long long)rows, s))) return rc;
+            // dOut rows with the geometry of the query-row map
+            {
+                const uint64_t row = (uint64_t)kHeadDim * 2, tok = (uint64_t)H * row;
+                uint64_t dqr[5] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)blk.w, (uint64_t)(n_q / blk.w), (uint64_t)B};
+                uint64_t sqr[4] = {row, tok, (uint64_t)blk.w * tok, (uint64_t)n_q * tok};
+                uint32_t bqr[5] = {64, 1, 1, (uint32_t)((blk.b1 + 3) / 4), 1};
+                if ((rc = make_tmap_bf16(&maps[6], dout, 5, dqr, sqr, bqr))) return rc;
+            }
+            CUtensorMap cmaps[4] = {maps[3], maps[4], maps[5], maps[6]};
+            if ((rc = launch_bwd_col_tc(mp, cmaps, delta, dcL, p.dq, status, num_sms, s))) return rc;
+            p.aLb = aLb; p.Yb = Yb; p.dcL = dcL; p.dcl_pitch = n_keys_c;
+        } else {
         {
             LaunchScope scope(kClsBackward, s);
             bwd_row_forward_kernel<<<dim3(pl.n_keys, nbh), 256, smem_fwd, s>>>(p);
@@ -763,6 +836,7 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
             else if (T == 4) bwd_col_kernel<4><<<grid, 256, smem_col, s>>>(p);
             else if (T == 8) bwd_col_kernel<8><<<grid, 256, smem_col, s>>>(p);
             else bwd_col_kernel<16><<<grid, 256, smem_col, s>>>(p);
+        }
         }
         {
             LaunchScope scope(kClsBackward, s);

@@ -77,7 +77,7 @@ def direct_check(sfb, c, ref, budget=0):
                                                          sm_scale=c["sm_scale"], budget_bytes=budget)
     torch.cuda.synchronize()
     assert dq.dtype == torch.float32
-    grad_close(dq, ref["q"], 2e-3, "dq")
+    grad_close(dq, ref["q"], 1e-2, "dq")      # aL, Y and their gradients pass through bf16, as in the reference
     # reference cache gradients are zero in the written slots; the kernels return the gradient w.r.t. the cache
     # CONTENT there, which is the new keys' gradient in Monarch order
     ft, hr, wr, h, w = c["blocking"]
