@@ -40,6 +40,10 @@ int forward_tc_slice(const void* q, int64_t q_bs, const void* kc, const void* vc
 int launch_bwd_delta(const void* dout, const void* out, float* delta, long long rows, cudaStream_t s);
 int launch_bwd_col_tc(const MonarchParams& mp, const CUtensorMap* maps, const float* delta, float* dcL, float* dq,
                       int* status, int num_sms, cudaStream_t s);
+size_t bwd_row_tc_partial_bytes(const MonarchParams& mp, int g0, int g1);
+int launch_bwd_row_tc(const MonarchParams& mp, const CUtensorMap* maps, const float* dcL, float* dq, float* part_k,
+                      float* part_v, __nv_bfloat16* dk, __nv_bfloat16* dv, int g0, int g1, int* status, int num_sms,
+                      cudaStream_t s);
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -705,6 +709,15 @@ int make_bwd_plan(BwdPlan* pl, int B, int H, int D, int n_q, int n_kv, int f_tie
     // the tensor-core path lays the same region out differently (bf16 bridge, log-sum-exp, a scratch output,
     // delta, a status word) and never needs more than this
     o += up256((size_t)B * n_q * H * (kHeadDim * 2 + 4)) + up256((size_t)pl->nbh * pl->A * blk.b2 * (blk.b1 + 8) * sizeof(float)) + 4096;
+    // its row kernel also keeps one fp32 copy of dK and dV per tile of stacked query groups (worst case: all cached
+    // groups wanted); the bf16 bridge leaves half of the fp32 one's space free for them
+    {
+        const int gpt = 128 / ((blk.b2 + 7) & ~7);
+        const size_t tiles = gpt > 0 ? (size_t)(pl->A + gpt - 1) / gpt : 0;
+        const size_t parts = 2 * (tiles * pl->nbh * (size_t)n_kv * kHeadDim * sizeof(float) + 256);
+        const size_t slack = units * kHeadDim * sizeof(float);
+        if (blk.b2 <= 64 && parts > slack) o += up256(parts - slack);
+    }
     pl->total = o;
     return SFM_OK;
 }
@@ -824,6 +837,24 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
             CUtensorMap cmaps[4] = {maps[3], maps[4], maps[5], maps[6]};
             if ((rc = launch_bwd_col_tc(mp, cmaps, delta, dcL, p.dq, status, num_sms, s))) return rc;
             p.aLb = aLb; p.Yb = Yb; p.dcL = dcL; p.dcl_pitch = n_keys_c;
+            // Row-step backward on tcgen05 when its per-tile dK / dV partials fit what is left of the workspace;
+            // SFM_BWD_ROW_FP32=1 keeps the fp32 row kernel.
+            const char* row_fp32 = getenv("SFM_BWD_ROW_FP32");
+            const size_t part = up256(bwd_row_tc_partial_bytes(mp, p.g0, p.g1));
+            if (!(row_fp32 && row_fp32[0] == '1') && o + 2 * part <= workspace_bytes) {
+                float* part_k = (float*)(ws + o);
+                float* part_v = (float*)(ws + o + part);
+                const int rows_per_group = (blk.b2 + 7) & ~7;
+                uint64_t db[3] = {(uint64_t)kHeadDim, (uint64_t)pl.n_keys, (uint64_t)slabs};
+                uint64_t sb[2] = {(uint64_t)kHeadDim * 2, (uint64_t)pl.n_keys * kHeadDim * 2};
+                uint32_t bb[3] = {64, 1, (uint32_t)rows_per_group};
+                CUtensorMap rmaps[5] = {maps[0], maps[1], maps[2]};
+                if ((rc = make_tmap_bf16(&rmaps[3], aLb, 3, db, sb, bb))) return rc;
+                if ((rc = make_tmap_bf16(&rmaps[4], Yb, 3, db, sb, bb))) return rc;
+                if ((rc = launch_bwd_row_tc(mp, rmaps, dcL, p.dq, part_k, part_v, p.dk, p.dv, p.g0, p.g1, status, num_sms, s)))
+                    return rc;
+                continue;
+            }
         } else {
         {
             LaunchScope scope(kClsBackward, s);
