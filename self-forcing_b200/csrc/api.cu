@@ -308,8 +308,8 @@ int forward_tc_slice(const void* q, int64_t q_bs, const void* kc, const void* vc
     const int rows_per_group = (blk.b2 + 7) & ~7;
     const int n_s = (blk.b2 + 15) & ~15;
     const size_t slabs = (size_t)nbh * p.A * blk.b2;
-    cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
-    if (e == cudaSuccess) e = cudaMemsetAsync(cL, 0x7f, slabs * p.n_keys_c * sizeof(float), stream);
+    // the caller owns the status word (set once per call, shared by its slices)
+    cudaError_t e = cudaMemsetAsync(cL, 0x7f, slabs * p.n_keys_c * sizeof(float), stream);
     if (e != cudaSuccess) return (int)e;
     int rc;
     const uint64_t row = (uint64_t)kHeadDim * 2, tok = (uint64_t)H * row;

@@ -18,8 +18,11 @@
 //                               the cached groups, own those rows in dq and in a second buffer merged afterwards:
 //                               no atomics),
 //                               dK[f,k,l] = sqrt(scale) sum_(a,j) (R_l daL + dz_l q^), dV[f,k,l] = sum_(a,j) R_l dY
-// The kernels are plain fp32 FMA code staged through shared memory: correct and deterministic, not yet on
-// the tensor cores.
+// The kernels of this file are plain fp32 FMA code staged through shared memory: deterministic, any block size
+// up to 128 x 128, block-causal mask included.  Without a mask and for block rows up to 32 and block columns up
+// to 64 the entry point runs the same three stages on the tensor cores instead (tcgen05): the forward's own row-
+// and column-step kernels for the recompute, then the column- and row-step backward kernels of
+// monarch_bwd_tc.cu / monarch_bwd_row_tc.cu, with aL, Y and their gradients in bf16 as in the reference.
 //
 // Stands in for _attention_with_cache.backward and its Triton kernels
 // (wan/modules/monarch_attn.py:403-596, 1034-1222, 1325-1470), including grad_only_new_kv
@@ -700,7 +703,7 @@ int make_bwd_plan(BwdPlan* pl, int B, int H, int D, int n_q, int n_kv, int f_tie
     const size_t per_bh = (size_t)pl->A * blk.b2 * pl->n_keys * (2 * kHeadDim + 2) * sizeof(float);
     pl->nbh = (int)std::max<size_t>(1, std::min<size_t>((size_t)B * H, budget / per_bh));
     const size_t units = (size_t)pl->nbh * pl->A * blk.b2 * pl->n_keys;
-    size_t o = 0;
+    size_t o = 256;                                   // the status word of the call sits at the start, in both layouts
     pl->off_aL = o; o = up256(o + units * kHeadDim * sizeof(float));
     pl->off_Y = o; o = up256(o + units * kHeadDim * sizeof(float));
     pl->off_cL = o; o = up256(o + units * sizeof(float));
@@ -799,6 +802,8 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
         int dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
+    // one status word per call: a kernel that gives up on a bounded wait sets it, nothing clears it before the end
+    if (cudaMemsetAsync(ws, 0, sizeof(int), s) != cudaSuccess) return SFM_ERR_UNSUPPORTED;
     for (int bh0 = 0; bh0 < BH; bh0 += pl.nbh) {
         const int nbh = std::min(pl.nbh, BH - bh0);
         p.bh0 = bh0;

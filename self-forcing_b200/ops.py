@@ -109,12 +109,13 @@ def check_device_status(device=None) -> None:
     """Synchronous form: waits for the work queued on the current stream and raises if the last Monarch
     attention call queued on it (on ``device``) left a non-zero status word."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(), int(_stream().value or 0), "monarch")
-    ws = _workspaces.get(key)                      # the workspace of the current stream
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
     lib = _lib.load()
     with torch.cuda.device(dev):
-        if ws is not None:
-            _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
+        for kind in ("monarch", "monarch_bwd"):      # the workspaces of the current stream
+            ws = _workspaces.get((index, int(_stream().value or 0), kind))
+            if ws is not None:
+                _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), f"sfm_workspace_status ({kind})")
         _lib.check(lib.sfm_dense_status(_stream()), "sfm_dense_status")
 
 
@@ -232,6 +233,10 @@ def monarch_attn_with_kv_cache_backward(q, k_cache, v_cache, grad_out, f_tied, h
                              h_reduce, w_reduce, h, w, float(sm_scale), g0, g1, int(causal_groups), budget_bytes,
                              _stream())
     _lib.check(rc, "sfm_monarch_bwd")
+    if os.environ.get("SFM_CHECK_STATUS") == "1":      # debugging aid: synchronises the stream
+        _lib.check(lib.sfm_workspace_status(_ptr(ws), _stream()), "sfm_workspace_status")
+    else:
+        _watch_status(ws)
     return dq, dk, dv
 
 

@@ -108,6 +108,30 @@ def test_backward_real_block_sizes(sfb, blocking, frames_q, cached):
     direct_check(sfb, c, oracle_grads(c))
 
 
+@pytest.mark.parametrize("blocking,frames_q,cached", [((1, 1, 1, 4, 24), 3, 4), ((1, 1, 1, 4, 40), 4, 5),
+                                                      ((1, 1, 1, 5, 64), 3, 3), ((1, 1, 1, 30, 52), 3, 3)],
+                         ids=["b2_24", "b2_40_two_tiles", "b2_64_two_tiles", "framewise_two_tiles"])
+def test_backward_tile_widths_and_stacking(sfb, blocking, frames_q, cached):
+    """Block columns 24 / 40 / 64 (the 32-, 48- and 64-wide instantiations of the tensor-core row-step backward;
+    16 is covered by the small blockings) and three or four query groups, which stack into two tiles of query
+    rows whose dK / dV shares are merged afterwards."""
+    c = make_case(blocking, frames_q, cached, B=1, H=2, seed=8250 + blocking[4])
+    direct_check(sfb, c, oracle_grads(c))
+
+
+def test_backward_row_kernels_agree(sfb, monkeypatch):
+    """The tensor-core row-step backward against the fp32 one on the same intermediate gradients (the fp32 kernel
+    rounds nothing but its inputs): both must sit within bf16 rounding of each other."""
+    c = make_case((1, 1, 1, 6, 40), 3, 4, B=2, H=2, seed=8260)
+    _, kv, vv = gpu_cache(sfb, c)
+    args = (c["q"].cuda(), kv, vv, c["g"].cuda(), *c["blocking"])
+    a = sfb.monarch_attn_with_kv_cache_backward(*args, sm_scale=c["sm_scale"])
+    monkeypatch.setenv("SFM_BWD_ROW_FP32", "1")
+    b = sfb.monarch_attn_with_kv_cache_backward(*args, sm_scale=c["sm_scale"])
+    for x, y, what in zip(a, b, ("dq", "dk", "dv")):
+        grad_close(x, y, 6e-3, what)
+
+
 def test_backward_is_deterministic_and_slicing_is_invisible(sfb):
     c = make_case((1, 1, 1, 6, 8), 2, 4, B=2, H=3, seed=8300)
     ref = oracle_grads(c)
