@@ -19,7 +19,7 @@
 //                               no atomics),
 //                               dK[f,k,l] = sqrt(scale) sum_(a,j) (R_l daL + dz_l q^), dV[f,k,l] = sum_(a,j) R_l dY
 // The kernels of this file are plain fp32 FMA code staged through shared memory: deterministic, any block size
-// up to 128 x 128, block-causal mask included.  Without a mask and for block rows up to 32 and block columns up
+// up to 128 x 128, block-causal mask included.  Without a mask and for block rows up to 96 and block columns up
 // to 64 the entry point runs the same three stages on the tensor cores instead (tcgen05): the forward's own row-
 // and column-step kernels for the recompute, then the column- and row-step backward kernels of
 // monarch_bwd_tc.cu / monarch_bwd_row_tc.cu, with aL, Y and their gradients in bf16 as in the reference.
@@ -776,10 +776,10 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
     p.aLb = p.Yb = nullptr;
     p.dcl_pitch = pl.n_keys;
     // Tensor-core path: recompute of the forward's row step (and of the column step, for its softmax statistics
-    // and output) on the forward's own tcgen05 kernels, column-step backward on tcgen05; block rows up to 32,
-    // query rows reachable by TMA, no block-causal mask.  SFM_BWD_FP32=1 keeps everything on the fp32 kernels.
+    // and output) on the forward's own tcgen05 kernels, column- and row-step backward on tcgen05; block rows up to 96,
+    // block columns up to 64, query rows reachable by TMA, no block-causal mask.  SFM_BWD_FP32=1 keeps everything on the fp32 kernels.
     const char* force_fp32 = getenv("SFM_BWD_FP32");
-    const bool use_tc = causal_groups == 0 && blk.b1 <= 32 && blk.b2 <= 64 && (blk.f_tied == 1 || blk.h_reduce == 1) &&
+    const bool use_tc = causal_groups == 0 && blk.b1 <= 96 && blk.b2 <= 64 && (blk.f_tied == 1 || blk.h_reduce == 1) &&
                         !(force_fp32 && force_fp32[0] == '1');
 
     const int T = blk.b1 <= 16 ? 2 : (blk.b1 <= 32 ? 4 : (blk.b1 <= 64 ? 8 : 16));
@@ -831,13 +831,17 @@ extern "C" int sfm_monarch_bwd(const void* q, int64_t q_batch_stride, const void
             // delta = dOut . out for every (token, head); the scratch output holds this slice's heads only, the
             // other heads' products are never read
             if ((rc = launch_bwd_delta(dout, out_s, delta, (long long)rows, s))) return rc;
-            // dOut rows with the geometry of the query-row map
+            // query rows of q and dOut for the column kernel: (d, head, column, row of the token grid, batch), boxes of
+            // 32 consecutive grid rows (fewer when the whole call has fewer)
             {
                 const uint64_t row = (uint64_t)kHeadDim * 2, tok = (uint64_t)H * row;
+                const uint32_t box_rows = (uint32_t)std::min(32, n_q / blk.w);
                 uint64_t dqr[5] = {(uint64_t)kHeadDim, (uint64_t)H, (uint64_t)blk.w, (uint64_t)(n_q / blk.w), (uint64_t)B};
-                uint64_t sqr[4] = {row, tok, (uint64_t)blk.w * tok, (uint64_t)n_q * tok};
-                uint32_t bqr[5] = {64, 1, 1, (uint32_t)((blk.b1 + 3) / 4), 1};
-                if ((rc = make_tmap_bf16(&maps[6], dout, 5, dqr, sqr, bqr))) return rc;
+                uint64_t sq_[4] = {row, tok, (uint64_t)blk.w * tok, (uint64_t)q_batch_stride * 2};
+                uint64_t sdo[4] = {row, tok, (uint64_t)blk.w * tok, (uint64_t)n_q * tok};
+                uint32_t bqr[5] = {64, 1, 1, box_rows, 1};
+                if ((rc = make_tmap_bf16(&maps[5], q, 5, dqr, sq_, bqr))) return rc;
+                if ((rc = make_tmap_bf16(&maps[6], dout, 5, dqr, sdo, bqr))) return rc;
             }
             CUtensorMap cmaps[4] = {maps[3], maps[4], maps[5], maps[6]};
             if ((rc = launch_bwd_col_tc(mp, cmaps, delta, dcL, p.dq, status, num_sms, s))) return rc;

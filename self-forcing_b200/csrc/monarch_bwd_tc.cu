@@ -8,21 +8,25 @@
 //   dP[i,n] = dOut[i] . Y[n]                      dS = P (dP - delta)
 //   dY[n]  = sum_i P[i,n] dOut[i]                 daL[n] = scale * sum_i dS[i,n] q[i]        dcL[n] = -sum_i dS[i,n]
 //   dq[i]  = scale * sum_n dS[i,n] aL[n]          (the row step's share of dQ is added by its own backward)
-// The KEYS sit on the M side of the tensor core (TMEM lane = key), the slab's b1 <= 32 queries on the N side, so
-// that dY, daL and dcL come out one key per lane, ready for row-wise stores:
+// The KEYS sit on the M side of the tensor core (TMEM lane = key), the slab's queries on the N side in chunks of
+// 32 rows (NC = 1, 2 or 3 chunks: block rows up to 96), so that dY, daL and dcL come out one key per lane, ready
+// for row-wise stores.  Per (key tile, chunk of query rows):
 //   S^T  = aL_tile Q^T,  dP^T = Y_tile dOut^T               two tcgen05.mma, operands in shared memory
 //   P^T, (scale dS)^T as bf16 over the S^T / dP^T columns     one thread per key; dcL from its registers
 //   dY_tile = P^T dOut,  daL_tile = (scale dS)^T Q            A from TMEM, B = the query-side rows, MN-major
 //   dq^T (+)= aL_tile^T (scale dS)^T                          A = the aL tile read MN-major, B = a bf16 copy of
 //                                                             (scale dS)^T in shared memory; accumulates over the slab
-// dY and daL are written over Y and aL in place (a tile is in shared memory before its rows are overwritten).
+// dY and daL accumulate over the chunks of a tile in TMEM, dq^T has 32 columns per chunk and accumulates over the
+// tiles.  dY and daL are written over Y and aL in place (a tile is in shared memory before its rows are overwritten).
 //
 // Warp roles (12 warps): 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2-3 idle, 4-7 and 8-11 = two warpgroups
-// that take even / odd tiles (element-wise pass, then the drain of the dY / daL accumulators; the group that
-// handled a slab's last tile also stores its dq).  Persistent CTAs over contiguous shares of the slab list.
+// that take even / odd (tile, chunk) steps (element-wise pass; the group that had a tile's last chunk then drains
+// the dY / daL accumulators and adds up dcL, and after a slab's last tile stores its dq).  Persistent CTAs over contiguous shares of the slab list.
 // All waits are bounded and report through the status word.
 //
 // Stands in for the Triton kernel _z_bwd and its preprocess (wan/modules/monarch_attn.py:852-886, 1034-1222).
+#include <algorithm>
+
 #include "monarch_params.cuh"
 #include "profile.cuh"
 #include "tc05.cuh"
@@ -36,7 +40,8 @@ namespace {
 constexpr int kStgB = 2;                     // (aL, Y) tile-pair ring
 constexpr int kThreadsB = 384;
 constexpr int kKB = 128;                     // keys per tile
-constexpr int kNI = 32;                      // query rows per slab, padded (block rows up to 32)
+constexpr int kNI = 32;                      // query rows per chunk
+constexpr int kMaxNC = 3;                    // chunks per slab: block rows up to 96
 constexpr uint32_t kTmemColsB = 512;
 // TMEM columns: per warpgroup S^T / P^T at w*64, dP^T / dS^T at w*64 + 32; accumulators after them
 __host__ __device__ constexpr uint32_t bc_s(int w) { return (uint32_t)w * 64u; }
@@ -55,7 +60,8 @@ struct BwdColParams {
     float* dq;                     // natural order [B, n_q, H, 128] fp32
     int H, n_q, A, n_keys, n_keys_c, bh0, nbh;
     int n_units;                   // nbh * A * b2
-    int R4, q_rows_tma;
+    int q_rows_tma;
+    int q_box_rows;                // rows per box of the q / dOut row maps (32, or all the grid rows there are)
     float scale;
     Blocking blk;
     int* status;
@@ -63,14 +69,15 @@ struct BwdColParams {
 
 constexpr int kQdHalf = kNI * 128;                 // one 64-column half of a query-side tile (32 rows)
 constexpr int kQdTile = 2 * kQdHalf;               // 8 KB
-constexpr int kQdBuf = 2 * kQdTile;                // q tile + dOut tile of one slab
+constexpr int kQdBuf = 2 * kQdTile;                // q rows + dOut rows of one chunk
 constexpr int kBTile = 2 * kKB * 128;              // one aL or Y tile, 32 KB
 constexpr int kBStage = 2 * kBTile;                // aL + Y
 constexpr int kDsTile = kKB * 128;                 // (scale dS)^T copy: 128 keys x 64 bf16, 16 KB
 
 struct __align__(16) BBarriers {
-    float lse2[2][kNI];
-    float delta[2][kNI];
+    float lse2[2][kMaxNC * kNI];
+    float delta[2][kMaxNC * kNI];
+    float dsum[2][kMaxNC][kKB];             // [tile parity][chunk][key]: -dcL shares of the chunks
     uint64_t q_full[2], q_empty[2];
     uint64_t a_full[kStgB], a_empty[kStgB];
     uint64_t s_full[2], p_full[2], sd_free[2];
@@ -80,7 +87,11 @@ struct __align__(16) BBarriers {
     volatile int abort_flag;
 };
 
-constexpr int kBSmemBytes = 1024 + 2 * kQdBuf + kStgB * kBStage + 2 * kDsTile + (int)sizeof(BBarriers) + 64;
+// query-side buffers: two slabs of one chunk (the next slab's rows load while this one is worked on), or one slab of NC
+__host__ __device__ constexpr int qd_bytes(int nc) { return (nc == 1 ? 2 : nc) * kQdBuf; }
+__host__ __device__ constexpr int b_smem_bytes(int nc) {
+    return 1024 + qd_bytes(nc) + kStgB * kBStage + 2 * kDsTile + (int)sizeof(BBarriers) + 64;
+}
 
 __device__ __forceinline__ void tmem_st16b(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
 __device__ __forceinline__ void stg_v8(void* ptr, const uint32_t (&w)[8]) {
@@ -97,28 +108,28 @@ __device__ __forceinline__ BUnit b_decode(const BwdColParams& p, int u) {
     return r;
 }
 
-// tal / ty = bridge maps (box 64 x 128 keys x 1); tqr / tdo = query rows of q / dOut (5-D, box rows = R4).
+// tal / ty = bridge maps (box 64 x 128 keys x 1); tqr / tdo = query rows of q / dOut (5-D, box of 32 rows).
+template <int NC>
 __global__ void __launch_bounds__(kThreadsB, 1)
 monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_constant__ CUtensorMap ty,
                           const __grid_constant__ CUtensorMap tqr, const __grid_constant__ CUtensorMap tdo,
                           BwdColParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* qd_s = base;                                   // [2 slabs][q tile | dOut tile]
-    unsigned char* a_s = qd_s + 2 * kQdBuf;                        // [stage][aL tile | Y tile]
+    unsigned char* qd_s = base;                                   // [slab buffer][chunk][q rows | dOut rows]
+    unsigned char* a_s = qd_s + qd_bytes(NC);                      // [stage][aL tile | Y tile]
     unsigned char* ds_s = a_s + kStgB * kBStage;                   // [warpgroup] (scale dS)^T, 128 rows of 128 bytes
     BBarriers* bars = reinterpret_cast<BBarriers*>(ds_s + 2 * kDsTile);
 
     const Blocking& blk = p.blk;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b1 = blk.b1, b2 = blk.b2;
+    const int b1 = blk.b1;
     const int n_keys = p.n_keys;
     const int n_tiles = (n_keys + kKB - 1) / kKB;
-    const int R4 = p.R4;
-    const long long tok_pitch = (long long)p.H * kHeadDim;
     const int u_begin = (int)((long long)p.n_units * blockIdx.x / gridDim.x);
     const int u_end = (int)((long long)p.n_units * (blockIdx.x + 1) / gridDim.x);
-    const int total = (u_end - u_begin) * n_tiles;
+    const int total = (u_end - u_begin) * n_tiles * NC;            // (slab, tile, chunk) steps of this CTA
+    constexpr int kQBufs = NC == 1 ? 2 : 1;
 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); }
@@ -132,7 +143,7 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
         mbar_init_fence();
     }
     // query-side rows no load writes, and the padding columns of the (scale dS)^T copies, must read as zero
-    for (int i = tid; i < (2 * kQdBuf + 0) / 16; i += kThreadsB) reinterpret_cast<uint4*>(qd_s)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < qd_bytes(NC) / 16; i += kThreadsB) reinterpret_cast<uint4*>(qd_s)[i] = make_uint4(0, 0, 0, 0);
     for (int i = tid; i < 2 * kDsTile / 16; i += kThreadsB) reinterpret_cast<uint4*>(ds_s)[i] = make_uint4(0, 0, 0, 0);
     if (warp == 1) { tmem_alloc(&bars->tmem_base, kTmemColsB); tmem_relinquish(); }
     fence_async_smem();
@@ -149,50 +160,15 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) { prefetch_tmap(&tal); prefetch_tmap(&ty); prefetch_tmap(&tqr); prefetch_tmap(&tdo); }
-        int g = 0, uc = 0;
+        int g = 0, uc = 0;                                       // tiles loaded, slabs started
         bool ok = true;
         for (int u = u_begin; ok && u < u_end && !bars->abort_flag; ++u, ++uc) {
             const BUnit un = b_decode(p, u);
             const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
-            const int qb = uc & 1;
+            const int qb = kQBufs == 2 ? (uc & 1) : 0;
             unsigned char* qt = qd_s + qb * kQdBuf;
-            if (uc >= 2) {
-                int okw = 1;
-                if (lane == 0) okw = mbar_wait(&bars->q_empty[qb], ((uc >> 1) - 1) & 1) ? 1 : 0;
-                if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(10); break; }
-            }
-            if (lane < kNI) {
-                const int i = lane;
-                float l2 = INFINITY, dl = 0.f;
-                if (i < b1) {
-                    const long long tok = blk.row_token(un.a, i) + un.j;
-                    l2 = kLog2e * p.lse[(long long)u * b1 + i];
-                    dl = p.delta[((long long)b * p.n_q + tok) * p.H + hd];
-                }
-                bars->lse2[qb][i] = l2;
-                bars->delta[qb][i] = dl;
-            }
-            if (p.q_rows_tma) {
-                __syncwarp();
-                if (lane == 0) {
-                    const int nq = (b1 + R4 - 1) / R4;
-                    mbar_arrive_expect_tx(&bars->q_full[qb], (uint32_t)(2 * nq * R4 * 256));
-                    const int tok0 = blk.row_token(un.a, 0);
-                    const int frow0 = tok0 / blk.w, col = tok0 - frow0 * blk.w + un.j;
-                    for (int qd = 0; qd < nq; ++qd) {
-                        unsigned char* dq_ = qt + (qd * R4) * 128;
-                        tma_load_5d(dq_, &tqr, &bars->q_full[qb], 0, hd, col, frow0 + qd * R4, b);
-                        tma_load_5d(dq_ + kQdHalf, &tqr, &bars->q_full[qb], 64, hd, col, frow0 + qd * R4, b);
-                        tma_load_5d(dq_ + kQdTile, &tdo, &bars->q_full[qb], 0, hd, col, frow0 + qd * R4, b);
-                        tma_load_5d(dq_ + kQdTile + kQdHalf, &tdo, &bars->q_full[qb], 64, hd, col, frow0 + qd * R4, b);
-                    }
-                }
-            } else {
-                fail(12);                      // the host only launches this kernel for blockings whose query rows come by TMA
-                break;
-            }
-            if (lane == 0) {
-                for (int t = 0; t < n_tiles; ++t, ++g) {
+            auto load_tiles = [&](int t_begin, int t_end) {      // lane 0 only
+                for (int t = t_begin; t < t_end; ++t, ++g) {
                     const int s = g % kStgB;
                     if (g >= kStgB && !mbar_wait(&bars->a_empty[s], ((g / kStgB) - 1) & 1)) { fail(11); ok = false; break; }
                     unsigned char* st = a_s + s * kBStage;
@@ -202,6 +178,41 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
                     tma_load_3d(st + kBTile, &ty, &bars->a_full[s], 0, t * kKB, u);
                     tma_load_3d(st + kBTile + kKB * 128, &ty, &bars->a_full[s], 64, t * kKB, u);
                 }
+            };
+            // the slab's first tile does not wait for the query-side buffer
+            if (lane == 0) load_tiles(0, 1);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            if (uc >= kQBufs) {
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(&bars->q_empty[qb], ((uc / kQBufs) - 1) & 1) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, okw, 0)) { fail(10); break; }
+            }
+            for (int i = lane; i < NC * kNI; i += 32) {
+                float l2 = INFINITY, dl = 0.f;
+                if (i < b1) {
+                    const long long tok = blk.row_token(un.a, i) + un.j;
+                    l2 = kLog2e * p.lse[(long long)u * b1 + i];
+                    dl = p.delta[((long long)b * p.n_q + tok) * p.H + hd];
+                }
+                bars->lse2[qb][i] = l2;
+                bars->delta[qb][i] = dl;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                // 32 consecutive rows of the token grid per chunk; rows past the slab's b1 hold other tokens (or the
+                // fill value) and are masked by an infinite log-sum-exp
+                mbar_arrive_expect_tx(&bars->q_full[qb], (uint32_t)(NC * 4 * p.q_box_rows * 128));
+                const int tok0 = blk.row_token(un.a, 0);
+                const int frow0 = tok0 / blk.w, col = tok0 - frow0 * blk.w + un.j;
+                for (int c = 0; c < NC; ++c) {
+                    unsigned char* dq_ = qt + c * kQdBuf;
+                    tma_load_5d(dq_, &tqr, &bars->q_full[qb], 0, hd, col, frow0 + c * kNI, b);
+                    tma_load_5d(dq_ + kQdHalf, &tqr, &bars->q_full[qb], 64, hd, col, frow0 + c * kNI, b);
+                    tma_load_5d(dq_ + kQdTile, &tdo, &bars->q_full[qb], 0, hd, col, frow0 + c * kNI, b);
+                    tma_load_5d(dq_ + kQdTile + kQdHalf, &tdo, &bars->q_full[qb], 64, hd, col, frow0 + c * kNI, b);
+                }
+                load_tiles(1, n_tiles);
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             g = __shfl_sync(0xffffffffu, g, 0);
@@ -218,15 +229,18 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
             const uint64_t q_mn0 = smem_desc_sw128(smem_addr(qd_s), kQdHalf, 1024);         // q / dOut rows, MN-major
             const uint64_t ds0 = smem_desc_sw128(smem_addr(ds_s), 16, 1024);                // (scale dS)^T copy, MN-major, N = 64
             bool ok = true;
+            // step g = ((slab, tile), chunk); its warpgroup is g & 1
             auto issue_s = [&](int g) -> bool {
-                const int uc = g / n_tiles, t = g - uc * n_tiles, w = g & 1, s = g % kStgB, qb = uc & 1;
-                if (t == 0 && !mbar_wait(&bars->q_full[qb], (uc >> 1) & 1)) { fail(20); return false; }
-                if (!mbar_wait(&bars->a_full[s], (g / kStgB) & 1)) { fail(21); return false; }
+                const int gt = g / NC, c = g - gt * NC;
+                const int uc = gt / n_tiles, t = gt - uc * n_tiles, w = g & 1, s = gt % kStgB;
+                const int qb = kQBufs == 2 ? (uc & 1) : 0;
+                if (t == 0 && c == 0 && !mbar_wait(&bars->q_full[qb], (uc / kQBufs) & 1)) { fail(20); return false; }
+                if (c == 0 && !mbar_wait(&bars->a_full[s], (gt / kStgB) & 1)) { fail(21); return false; }
                 if (g >= 2 && !mbar_wait(&bars->sd_free[w], ((g >> 1) - 1) & 1)) { fail(22); return false; }
                 tc_fence_after();
                 const uint64_t al = a_k0 + (uint64_t)((s * kBStage) >> 4);
                 const uint64_t yy = al + (uint64_t)(kBTile >> 4);
-                const uint64_t qq = q_k0 + (uint64_t)((qb * kQdBuf) >> 4);
+                const uint64_t qq = q_k0 + (uint64_t)(((qb + c) * kQdBuf) >> 4);
                 const uint64_t dd = qq + (uint64_t)(kQdTile >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
@@ -243,32 +257,47 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
                 mma_commit(&bars->s_full[w]);
                 return true;
             };
+            int drains[2] = {0, 0};               // accumulator hand-overs to each warpgroup so far
+            int last_drainer = 0;
             if (total > 0) ok = issue_s(0);
             for (int g = 0; ok && g < total && !bars->abort_flag; ++g) {
-                if (g + 1 < total && !issue_s(g + 1)) { ok = false; break; }
-                const int uc = g / n_tiles, t = g - uc * n_tiles, w = g & 1, s = g % kStgB, qb = uc & 1;
+                // The S GEMMs of the next step are issued ahead of this step's, except across a slab boundary when the
+                // query-side rows are single buffered: the next slab's rows can only load once this slab's last
+                // GEMMs have released the buffer, so waiting for them here would never end.
+                const bool ahead = g + 1 < total && !(kQBufs == 1 && (g + 1) % (n_tiles * NC) == 0);
+                if (ahead && !issue_s(g + 1)) { ok = false; break; }
+                const int gt = g / NC, c = g - gt * NC;
+                const int uc = gt / n_tiles, t = gt - uc * n_tiles, w = g & 1, s = gt % kStgB;
+                const int qb = kQBufs == 2 ? (uc & 1) : 0;
                 if (!mbar_wait(&bars->p_full[w], (g >> 1) & 1)) { fail(23); break; }
-                // the accumulators are shared: the other warpgroup must have drained the previous tile
-                if (g >= 1 && !mbar_wait(&bars->acc_free[(g - 1) & 1], ((g - 1) >> 1) & 1)) { fail(24); break; }
-                if (t == 0 && uc >= 1 && !mbar_wait(&bars->dq_free, (uc - 1) & 1)) { fail(25); break; }
+                // the accumulators are shared by all tiles: the previous tile's must have been drained
+                if (c == 0 && gt >= 1 && !mbar_wait(&bars->acc_free[last_drainer], (drains[last_drainer] - 1) & 1)) { fail(24); break; }
+                if (t == 0 && c == 0 && uc >= 1 && !mbar_wait(&bars->dq_free, (uc - 1) & 1)) { fail(25); break; }
                 tc_fence_after();
-                const uint64_t qn = q_mn0 + (uint64_t)((qb * kQdBuf) >> 4);
+                const uint64_t qn = q_mn0 + (uint64_t)(((qb + c) * kQdBuf) >> 4);
                 const uint64_t dn = qn + (uint64_t)(kQdTile >> 4);
 #pragma unroll
-                for (int kk = 0; kk < kNI / 16; ++kk)          // dY_tile = P^T dOut
-                    mma_ts(tmem + kColDY, tmem + bc_s(w) + kk * 8, dn + ((kk * 2048) >> 4), idesc_o, kk > 0);
+                for (int kk = 0; kk < kNI / 16; ++kk)          // dY_tile (+)= P^T dOut
+                    mma_ts(tmem + kColDY, tmem + bc_s(w) + kk * 8, dn + ((kk * 2048) >> 4), idesc_o, (c > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < kNI / 16; ++kk)          // daL_tile = (scale dS)^T Q
-                    mma_ts(tmem + kColDaL, tmem + bc_dp(w) + kk * 8, qn + ((kk * 2048) >> 4), idesc_o, kk > 0);
+                for (int kk = 0; kk < kNI / 16; ++kk)          // daL_tile (+)= (scale dS)^T Q
+                    mma_ts(tmem + kColDaL, tmem + bc_dp(w) + kk * 8, qn + ((kk * 2048) >> 4), idesc_o, (c > 0 || kk > 0) ? 1u : 0u);
                 const uint64_t am = a_mn0 + (uint64_t)((s * kBStage) >> 4);
                 const uint64_t dsd = ds0 + (uint64_t)((w * kDsTile) >> 4);
+                // dq^T of chunk c (+)= aL_tile^T (scale dS)^T: 64 output columns of which the upper 32 receive zeros
+                // (and, on a slab's first tile, are set to zero before the next chunk sets its own)
 #pragma unroll
-                for (int kk = 0; kk < kKB / 16; ++kk)          // dq^T (+)= aL_tile^T (scale dS)^T
-                    mma_ss(tmem + kColDq, am + ((kk * 2048) >> 4), dsd + ((kk * 2048) >> 4), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
-                mma_commit(&bars->acc_full[w]);
+                for (int kk = 0; kk < kKB / 16; ++kk)
+                    mma_ss(tmem + kColDq + c * kNI, am + ((kk * 2048) >> 4), dsd + ((kk * 2048) >> 4), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
+                if (c == NC - 1) {
+                    mma_commit(&bars->acc_full[w]);
+                    ++drains[w];
+                    last_drainer = w;
+                    mma_commit(&bars->a_empty[s]);
+                }
                 mma_commit(&bars->sd_free[w]);
-                mma_commit(&bars->a_empty[s]);
-                if (t + 1 == n_tiles) { mma_commit(&bars->dq_full); mma_commit(&bars->q_empty[qb]); }
+                if (t + 1 == n_tiles && c == NC - 1) { mma_commit(&bars->dq_full); mma_commit(&bars->q_empty[qb]); }
+                if (g + 1 < total && !ahead && !issue_s(g + 1)) { ok = false; break; }
             }
         }
     } else if (warp >= 4) {
@@ -279,8 +308,11 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
         const float scale_l2 = p.scale * kLog2e;
         unsigned char* ds_row = ds_s + w * kDsTile + row * 128;
+        int my_drains = 0;
         for (int g = w; g < total && !bars->abort_flag; g += 2) {
-            const int uc = g / n_tiles, t = g - uc * n_tiles, qb = uc & 1;
+            const int gt = g / NC, c = g - gt * NC;
+            const int uc = gt / n_tiles, t = gt - uc * n_tiles;
+            const int qb = kQBufs == 2 ? (uc & 1) : 0;
             const int u = u_begin + uc;
             const int key = t * kKB + row;
             const bool valid = key < n_keys;
@@ -291,35 +323,43 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
             tmem_ld32(tmem + lane_sel + bc_s(w), rs);
             tmem_ld32(tmem + lane_sel + bc_dp(w), rd);
             tmem_wait_ld();
-            const float* lse2 = bars->lse2[qb];
-            const float* dlt = bars->delta[qb];
+            const float* lse2 = bars->lse2[qb] + c * kNI;
+            const float* dlt = bars->delta[qb] + c * kNI;
             float dsum = 0.f;
             uint32_t pp[kNI / 2], pd[kNI / 2];
 #pragma unroll
-            for (int c = 0; c < kNI; c += 2) {
-                const float p0 = exp2f(fmaf(__uint_as_float(rs[c]), scale_l2, -(cl2 + lse2[c])));
-                const float p1 = exp2f(fmaf(__uint_as_float(rs[c + 1]), scale_l2, -(cl2 + lse2[c + 1])));
-                const float d0 = p0 * (__uint_as_float(rd[c]) - dlt[c]);
-                const float d1 = p1 * (__uint_as_float(rd[c + 1]) - dlt[c + 1]);
+            for (int cc = 0; cc < kNI; cc += 2) {
+                const float p0 = exp2f(fmaf(__uint_as_float(rs[cc]), scale_l2, -(cl2 + lse2[cc])));
+                const float p1 = exp2f(fmaf(__uint_as_float(rs[cc + 1]), scale_l2, -(cl2 + lse2[cc + 1])));
+                const float d0 = p0 * (__uint_as_float(rd[cc]) - dlt[cc]);
+                const float d1 = p1 * (__uint_as_float(rd[cc + 1]) - dlt[cc + 1]);
                 dsum += d0 + d1;
-                pp[c >> 1] = pack_bf16(p0, p1);
-                pd[c >> 1] = pack_bf16(d0 * p.scale, d1 * p.scale);
+                pp[cc >> 1] = pack_bf16(p0, p1);
+                pd[cc >> 1] = pack_bf16(d0 * p.scale, d1 * p.scale);
             }
             tmem_st16b(tmem + lane_sel + bc_s(w), pp);
             tmem_st16b(tmem + lane_sel + bc_dp(w), pd);
             // bf16 copy of this key's (scale dS) row for the dq GEMM: 64 bytes of data, 128-byte swizzled row
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4*>(ds_row + ((c ^ (row & 7)) << 4)) = make_uint4(pd[4 * c], pd[4 * c + 1], pd[4 * c + 2], pd[4 * c + 3]);
+            for (int cc = 0; cc < 4; ++cc)
+                *reinterpret_cast<uint4*>(ds_row + ((cc ^ (row & 7)) << 4)) = make_uint4(pd[4 * cc], pd[4 * cc + 1], pd[4 * cc + 2], pd[4 * cc + 3]);
+            bars->dsum[gt & 1][c][row] = dsum;
             fence_async_smem();
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars->p_full[w]);
-            if (valid) p.dcL[(long long)u * p.n_keys_c + key] = -dsum;
+            if (c != NC - 1) continue;
 
-            // ---- drain dY and daL of this tile: one 256-byte row each, written over Y and aL
-            if (!mbar_wait(&bars->acc_full[w], (g >> 1) & 1)) { fail(41); break; }
+            // ---- the tile's last chunk: drain dY and daL, one 256-byte row each, written over Y and aL
+            if (!mbar_wait(&bars->acc_full[w], my_drains & 1)) { fail(41); break; }
+            ++my_drains;
             tc_fence_after();
+            if (valid) {
+                float acc = 0.f;                     // the chunks' shares in a fixed order
+#pragma unroll
+                for (int cc = 0; cc < NC; ++cc) acc += bars->dsum[gt & 1][cc][row];
+                p.dcL[(long long)u * p.n_keys_c + key] = -acc;
+            }
             const long long ro = ((long long)u * n_keys + key) * kHeadDim;
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
@@ -350,17 +390,24 @@ monarch_bwd_col_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_
             if (t + 1 == n_tiles) {
                 if (!mbar_wait(&bars->dq_full, uc & 1)) { fail(42); break; }
                 tc_fence_after();
-                uint32_t r[kNI];
-                tmem_ld32(tmem + lane_sel + kColDq, r);
+                uint32_t r[NC][kNI];
+#pragma unroll
+                for (int cc = 0; cc < NC; ++cc) tmem_ld32(tmem + lane_sel + kColDq + cc * kNI, r[cc]);
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(&bars->dq_free);
                 const BUnit un = b_decode(p, u);
                 const int bh = p.bh0 + un.bhl, b = bh / p.H, hd = bh - b * p.H;
-#pragma unroll 1
-                for (int i = 0; i < b1; ++i) {
-                    const long long tok = blk.row_token(un.a, i) + un.j;
-                    p.dq[(((long long)b * p.n_q + tok) * p.H + hd) * kHeadDim + row] = __uint_as_float(r[i]);
+#pragma unroll
+                for (int cc = 0; cc < NC; ++cc) {
+#pragma unroll
+                    for (int ii = 0; ii < kNI; ++ii) {
+                        const int i = cc * kNI + ii;
+                        if (i < b1) {
+                            const long long tok = blk.row_token(un.a, i) + un.j;
+                            p.dq[(((long long)b * p.n_q + tok) * p.H + hd) * kHeadDim + row] = __uint_as_float(r[cc][ii]);
+                        }
+                    }
                 }
             }
         }
@@ -397,10 +444,11 @@ int launch_bwd_delta(const void* dout, const void* out, float* delta, long long 
     return (int)cudaGetLastError();
 }
 
-// Column-step backward for one slice of (batch, head) pairs.  maps = {aL bridge, Y bridge, q rows, dOut rows}.
+// Column-step backward for one slice of (batch, head) pairs.  maps = {aL bridge, Y bridge, q rows, dOut rows}; the
+// two row maps are 5-D (d, head, column, row of the token grid, batch) with boxes of 32 rows.
 int launch_bwd_col_tc(const MonarchParams& mp, const CUtensorMap* maps, const float* delta, float* dcL, float* dq,
                       int* status, int num_sms, cudaStream_t s) {
-    if (mp.blk.b1 > kNI) return SFM_ERR_UNSUPPORTED;
+    if (mp.blk.b1 > kMaxNC * kNI) return SFM_ERR_UNSUPPORTED;
     LaunchScope scope(kClsBackward, s);
     BwdColParams p;
     p.q = mp.q; p.q_bs = mp.q_bs; p.delta = delta; p.lse = mp.lse;
@@ -408,16 +456,23 @@ int launch_bwd_col_tc(const MonarchParams& mp, const CUtensorMap* maps, const fl
     p.H = mp.H; p.n_q = mp.n_q; p.A = mp.na; p.n_keys = mp.n_keys; p.n_keys_c = mp.n_keys_c;
     p.bh0 = mp.bh0; p.nbh = mp.nbh;
     p.n_units = mp.nbh * mp.na * mp.blk.b2;
-    p.R4 = (mp.blk.b1 + 3) / 4;
+    p.q_box_rows = std::min(32, mp.n_q / mp.blk.w);
     p.q_rows_tma = (mp.blk.f_tied == 1 || mp.blk.h_reduce == 1) ? 1 : 0;
     if (!p.q_rows_tma) return SFM_ERR_UNSUPPORTED;
     p.scale = mp.scale;
     p.blk = mp.blk;
     p.status = status;
     dim3 grid(p.n_units < num_sms ? p.n_units : num_sms);
-    cudaError_t e = cudaFuncSetAttribute(monarch_bwd_col_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBSmemBytes);
-    if (e != cudaSuccess) return (int)e;
-    monarch_bwd_col_tc_kernel<<<grid, kThreadsB, kBSmemBytes, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+    const int nc = (mp.blk.b1 + kNI - 1) / kNI;
+    auto go = [&](auto kernel, int smem) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<grid, kThreadsB, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+        return 0;
+    };
+    int rc = nc == 1 ? go(monarch_bwd_col_tc_kernel<1>, b_smem_bytes(1))
+                     : (nc == 2 ? go(monarch_bwd_col_tc_kernel<2>, b_smem_bytes(2)) : go(monarch_bwd_col_tc_kernel<3>, b_smem_bytes(3)));
+    if (rc) return rc;
     return (int)cudaGetLastError();
 }
 

@@ -109,12 +109,16 @@ def test_backward_real_block_sizes(sfb, blocking, frames_q, cached):
 
 
 @pytest.mark.parametrize("blocking,frames_q,cached", [((1, 1, 1, 4, 24), 3, 4), ((1, 1, 1, 4, 40), 4, 5),
-                                                      ((1, 1, 1, 5, 64), 3, 3), ((1, 1, 1, 30, 52), 3, 3)],
-                         ids=["b2_24", "b2_40_two_tiles", "b2_64_two_tiles", "framewise_two_tiles"])
+                                                      ((1, 1, 1, 5, 64), 3, 3), ((1, 1, 1, 30, 52), 3, 3),
+                                                      ((1, 1, 1, 40, 24), 2, 4), ((3, 1, 1, 30, 52), 1, 2),
+                                                      ((2, 1, 1, 33, 16), 2, 5)],
+                         ids=["b2_24", "b2_40_two_tiles", "b2_64_two_tiles", "framewise_two_tiles",
+                              "b1_40_two_chunks", "tied3frame_three_chunks_two_key_tiles", "b1_66_three_chunks"])
 def test_backward_tile_widths_and_stacking(sfb, blocking, frames_q, cached):
     """Block columns 24 / 40 / 64 (the 32-, 48- and 64-wide instantiations of the tensor-core row-step backward;
     16 is covered by the small blockings) and three or four query groups, which stack into two tiles of query
-    rows whose dK / dV shares are merged afterwards."""
+    rows whose dK / dV shares are merged afterwards; block rows 40 / 66 / 90, i.e. two and three 32-row chunks
+    in the column-step backward, over one to three key tiles."""
     c = make_case(blocking, frames_q, cached, B=1, H=2, seed=8250 + blocking[4])
     direct_check(sfb, c, oracle_grads(c))
 
