@@ -357,6 +357,15 @@ int sfm_profile_read(float* ms, long long* launches, int n_classes);
  */
 int sfm_probe_dsmem_store(int cluster, int pattern, int remote, int iters, float* ms, int* ctas, double* bytes);
 
+/*
+ * Self-test of the failure path (no counterpart in the reference, whose kernels have no device-side waits): one
+ * small CTA allocates tensor memory as the attention kernels do and waits, for `polls` polls (1 .. 65536), on an
+ * mbarrier nothing arrives at.  The wait runs out, the kernel stores `code` (1 .. 255) in the status word at the
+ * start of `workspace` (cleared first), releases its tensor memory and returns; sfm_workspace_status(workspace,
+ * stream) then reports SFM_ERR_DEVICE_STATUS and the context stays usable.  Nothing faults or traps.
+ */
+int sfm_selftest_bounded_wait(void* workspace, int polls, int code, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

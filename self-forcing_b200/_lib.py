@@ -50,6 +50,7 @@ SIGNATURES = {
     "sfm_profile_enable": (C.c_int, [C.c_int]),
     "sfm_profile_read": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "sfm_probe_dsmem_store": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sfm_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
 }
 
 _lib = None

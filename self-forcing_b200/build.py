@@ -17,7 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libsfmonarch.so"
 SOURCES = ["layout.cu", "tmap.cu", "monarch_rstep.cu", "monarch_rstep_tc.cu", "monarch_lstep.cu", "monarch_lstep_tc.cu", "monarch_iter_tc.cu", "dense.cu",
-           "monarch_bwd.cu", "monarch_bwd_tc.cu", "monarch_bwd_row_tc.cu", "probe_dsmem.cu", "api.cu"]
+           "monarch_bwd.cu", "monarch_bwd_tc.cu", "monarch_bwd_row_tc.cu", "probe_dsmem.cu", "selftest.cu", "api.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -31,10 +31,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
-// Returns false if the phase did not complete within the poll limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Returns false if the phase did not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint32_t limit) {
     uint32_t addr = smem_addr(bar);
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\n"
@@ -45,6 +45,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, kSpinLimit); }
 
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {

@@ -609,6 +609,34 @@ def test_status_watch_without_synchronising(sfb, monkeypatch):
 
 
 @pytest.mark.gpu
+def test_bounded_wait_runs_out_and_reports(sfb):
+    """A device-side wait that nothing satisfies: the library's self-test kernel allocates tensor memory, waits a
+    few thousand polls on an mbarrier nobody arrives at, gives up, stores its code in the workspace's status word,
+    releases the tensor memory and returns.  The host then sees SFM_ERR_DEVICE_STATUS through the same reader the
+    attention calls use, the context is still usable, and the next attention call on that workspace clears the
+    word and is bit-equal to one made before."""
+    from self_forcing_b200 import _lib, ops
+    lib = _lib.load()
+    c = small_case(0, 1)
+    ref, _, _ = run_gpu_cache(sfb, c)
+    torch.cuda.synchronize()
+    dev = torch.cuda.current_device()
+    ws = ops._workspaces[(dev, int(ops._stream().value or 0), "monarch")]
+    assert lib.sfm_workspace_status(ops._ptr(ws), ops._stream()) == 0
+    _lib.check(lib.sfm_selftest_bounded_wait(ops._ptr(ws), 4096, 77, ops._stream()), "sfm_selftest_bounded_wait")
+    assert int(ws[:4].view(torch.int32)[0]) == 77
+    assert lib.sfm_workspace_status(ops._ptr(ws), ops._stream()) == -7          # SFM_ERR_DEVICE_STATUS
+    with pytest.raises(RuntimeError):
+        ops.check_device_status()
+    again, _, _ = run_gpu_cache(sfb, c)
+    torch.cuda.synchronize()
+    assert lib.sfm_workspace_status(ops._ptr(ws), ops._stream()) == 0
+    assert torch.equal(ref, again)
+    assert lib.sfm_selftest_bounded_wait(ops._ptr(ws), 0, 77, ops._stream()) == -2       # argument checks
+    assert lib.sfm_selftest_bounded_wait(None, 16, 77, ops._stream()) == -1
+
+
+@pytest.mark.gpu
 def test_two_streams_use_separate_workspaces(sfb):
     """Calls queued on different streams may overlap on the GPU: each stream gets its own scratch, and both
     results equal the single-stream one."""
