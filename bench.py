@@ -181,7 +181,7 @@ def make_inputs(k: int, seed: int, device, heads: int = HEADS):
     return q, kn, vn, caches
 
 
-def make_step(sfb, blocking, k, q, kn, vn, caches):
+def make_step(sfb, blocking, k, q, kn, vn, caches, num_iters=1):
     n_kv = k * CHUNK
     start = n_kv - CHUNK
     start_frame = CHUNK_FRAMES * (k - 1)
@@ -198,7 +198,7 @@ def make_step(sfb, blocking, k, q, kn, vn, caches):
         def step(qd=q, kd=kn, vd=vn):
             kc, vc = caches[state["i"] % len(caches)]; state["i"] += 1
             return sfb.rope_monarch_attn_with_kv_cache(qd, kd, vd, kc[:, :n_kv], vc[:, :n_kv], start, n_kv,
-                                                       start_frame, ft, hr, wr, H_GRID, W_GRID)
+                                                       start_frame, ft, hr, wr, H_GRID, W_GRID, num_iters=num_iters)
     return step
 
 
@@ -289,7 +289,8 @@ def run_reference_arm(args, rank, world):
 
 def workload_config(args):
     return {"workload": f"Wan-1.3B self-attention op, {args.blocking}, 4680-token chunk vs {args.k * CHUNK}-token "
-                        f"KV cache (k={args.k}), 12 heads x 128, B=1 per GPU, RoPE 44/42/42 fused",
+                        f"KV cache (k={args.k}), 12 heads x 128, B=1 per GPU, RoPE 44/42/42 fused"
+                        + (f", {args.num_iters} alternating passes" if getattr(args, "num_iters", 1) > 1 else ""),
             "blocking": args.blocking, "k": args.k, "n_q": CHUNK, "n_kv": args.k * CHUNK, "heads": HEADS,
             "head_dim": HEAD_DIM, "l2": f"{N_LAYER_CACHES} rotating layer caches "
                                          f"({N_LAYER_CACHES * 2 * args.k * CHUNK * HEADS * HEAD_DIM * 2 / 1e6:.0f} MB) "
@@ -719,7 +720,7 @@ def main():
                     help="with --model and N > 1 GPUs: one video over all GPUs (sequence parallel outside attention, head "
                          "sharding inside) instead of independent videos per GPU")
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the number of blocks (0 = the model's)")
-    ap.add_argument("--num-iters", type=int, default=1, help="with --model: MONARCH_ATTN_NUM_ITERS")
+    ap.add_argument("--num-iters", type=int, default=1, help="alternating passes T of the Monarch op (with --model: MONARCH_ATTN_NUM_ITERS); the roofline figures assume T = 1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -781,7 +782,7 @@ def main():
 
     q, kn, vn, caches = make_inputs(args.k, 100 + rank, device)
     qd, kd, vd = q.to(device), kn.to(device), vn.to(device)
-    step = make_step(sfb, args.blocking, args.k, qd, kd, vd, caches)
+    step = make_step(sfb, args.blocking, args.k, qd, kd, vd, caches, args.num_iters)
 
     # ---- headline: device-resident inputs -------------------------------------------------
     def reduce_max(ms):

@@ -258,7 +258,7 @@ int run_monarch(const void* q, int64_t q_bs, const void* kc, const void* vc, int
                 } else if (iter_tc) {
                     // the column step's softmax statistics (its output row is overwritten by the last pass), then
                     // the update of the state
-                    if ((rc = launch_l_step_tc(p, maps + 3, status, num_sms, stream, 1))) return rc;
+                    if ((rc = launch_l_step_tc(p, maps + 3, status, num_sms, stream, 2))) return rc;
                     if ((rc = launch_l_iter_tc(p, &maps[3], &maps[5], status, num_sms, stream))) return rc;
                 } else {
                     if ((rc = launch_l_step(p, 1, stream))) return rc;

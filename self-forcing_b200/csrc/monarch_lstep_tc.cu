@@ -53,6 +53,7 @@ struct LTcParams {
     int n_kv;        // dense: keys per (batch, head)
     int q_tiles;     // dense: ceil(n_q / 128)
     int write_lse;   // column step: also store the log-sum-exp of every query row (iterative variant)
+    int lse_only;    // column step: nothing but that (no value tiles, no PV GEMMs, no output rows)
     int* status;
 };
 
@@ -296,7 +297,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         }
     } else if (warp == 3) {
         // ------------------------------------------------------------------ value-tile producer
-        if (lane == 0) {
+        if (lane == 0 && !lp.lse_only) {
             prefetch_tmap(&ty);
             int gy = 0;
             bool ok = true;
@@ -377,7 +378,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     // first GEMM of the group into this accumulator overwrites it: the previous group's
                     // result must have been read
                     if (t < 2 && gc > 0 && !mbar_wait(&bars->o_free, (gc - 1) & 1)) { fail(23); ok = false; break; }
-                    for (int us = 0; us < nu; ++us, ++gy) {
+                    for (int us = 0; us < nu && !lp.lse_only; ++us, ++gy) {
                         const int sy = gy % kYStages;
                         if (!mbar_wait(&bars->y_full[sy], (gy / kYStages) & 1)) { fail(26); ok = false; break; }
                         tc_fence_after();
@@ -501,7 +502,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                         lsum2 = f2_add(lsum2, f2_pack(e0, e1));
                         pk[c >> 1] = pack_bf16_alu(e0, e1);
                     }
-                    tmem_st16(s_t + (c0 >> 1), pk);
+                    if (!lp.lse_only) tmem_st16(s_t + (c0 >> 1), pk);
                 }
                 tmem_wait_st();
                 float lsum, lsum_hi;
@@ -563,14 +564,16 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
 #pragma unroll 1
             for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
                 uint32_t ra[32], rb[32];
-                tmem_ld32(tmem + lane_sel + col_o(0) + c0, ra);
-                tmem_ld32(tmem + lane_sel + col_o(1) + c0, rb);
-                tmem_wait_ld();
+                if (!lp.lse_only) {
+                    tmem_ld32(tmem + lane_sel + col_o(0) + c0, ra);
+                    tmem_ld32(tmem + lane_sel + col_o(1) + c0, rb);
+                    tmem_wait_ld();
+                }
                 if (c0 + 32 == kHeadDim) {
                     tc_fence_before();
                     mbar_arrive(&bars->o_free);               // accumulators and statistics are in registers
                 }
-                if (row_ok) {
+                if (row_ok && !lp.lse_only) {
 #pragma unroll
                     for (int v8 = 0; v8 < 2; ++v8) {
                         uint32_t wv[8];
@@ -615,7 +618,8 @@ int launch_l_step_tc(const MonarchParams& p, const CUtensorMap* maps /* aL, Y, q
     lp.q_rows_tma = (p.blk.f_tied == 1 || p.blk.h_reduce == 1) ? 1 : 0;
     lp.n_kv = 0;
     lp.q_tiles = 0;
-    lp.write_lse = write_lse;
+    lp.write_lse = write_lse != 0;
+    lp.lse_only = write_lse == 2;
     const int n_groups = (lp.n_units + lp.U - 1) / lp.U;
     dim3 grid(n_groups < num_sms ? n_groups : num_sms);
     auto kernel = p.causal_groups > 0 ? monarch_l_tc_kernel<false, true> : monarch_l_tc_kernel<false, false>;
@@ -644,6 +648,7 @@ int launch_dense_tc(const CUtensorMap* maps, __nv_bfloat16* out, int B, int H, i
     lp.n_kv = n_kv;
     lp.q_rows_tma = 1;
     lp.write_lse = 0;
+    lp.lse_only = 0;
     lp.status = status;
     dim3 grid(lp.n_units < num_sms ? lp.n_units : num_sms);
     cudaError_t e = cudaFuncSetAttribute(monarch_l_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

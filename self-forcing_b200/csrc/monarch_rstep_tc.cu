@@ -240,7 +240,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------------ PV-GEMM issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_o = idesc_bf16(kTileRows, 2 * kHeadDim, 0, 1);
+            // [aL | Y] in one N = 256 GEMM; the passes of the iterative variant that only need aL and cL stop at N = 128
+            const uint32_t idesc_o = p.write_Y ? idesc_bf16(kTileRows, 2 * kHeadDim, 0, 1) : idesc_bf16(kTileRows, kHeadDim, 0, 1);
             constexpr int ksteps_pv = N_S / 16;
             const uint64_t kv_desc_mn0 = smem_desc_sw128(smem_addr(kv_s), kHalf, 1024);   // 4 column blocks: K lo, K hi, V lo, V hi
             int g = 0;
@@ -456,14 +457,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 tc_fence_after();
                 // This thread's bridge row: 256 bytes at (aj, key), written as 32-byte vectors.
                 const int gl = row / RG, j = row - gl * RG;
-                const bool row_ok = warp_active && gl < ng && j < b2;
+                const bool row_ok = warp_active && gl < ng && j < b2 && (which == 0 || p.write_Y);
                 const long long aj = ((long long)un.bhl * p.na + g_first + gl) * b2 + j;
                 const int key = (un.f_begin + i) * b1 + un.k;
                 __nv_bfloat16* const out_row = (which ? p.Y : p.aL) + (aj * p.n_keys + key) * kHeadDim;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {                 // 64 columns at a time
                     uint32_t ra[32], rb[32];
-                    if (warp_active) {
+                    if (warp_active && (which == 0 || p.write_Y)) {
                         tmem_ld32(o_t + h * 64, ra);
                         tmem_ld32(o_t + h * 64 + 32, rb);
                         tmem_wait_ld();
