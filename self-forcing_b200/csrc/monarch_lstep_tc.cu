@@ -65,7 +65,7 @@ struct __align__(16) Barriers {
     uint64_t a_full[kAStages], a_empty[kAStages];
     uint64_t y_full[kYStages], y_empty[kYStages];
     uint64_t cl_full[4], cl_empty[4];
-    uint64_t s_full[2], p_full[2], sp_free[2];
+    uint64_t s_full[4], p_full[4], sp_free[4];   // [warpgroup * 2 + half]: dense attention works on 64-key halves of a tile
     uint64_t pv_done[2];                   // all PV GEMMs issued so far into accumulator w have completed
     uint64_t o_full, o_free;
     uint32_t tmem_base;
@@ -122,6 +122,11 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     const Blocking& blk = p.blk;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b1 = blk.b1, b2 = blk.b2;
+    // Dense attention splits every 128-key tile into two 64-key halves with an S / P buffer each (64 columns), so that
+    // the S GEMM of one half runs while the other half's softmax does; the column step, bound by its bridge reads,
+    // keeps whole tiles.
+    constexpr int kH = kDense ? 2 : 1;
+    constexpr int kNS = kKT / kH;
     const int n_keys = kDense ? lp.n_kv : p.n_keys;
     const int n_tiles_all = (n_keys + kKT - 1) / kKT;
     // Key tiles a group of units has to walk.  Block-causal (no-cache path): the keys past the last cached
@@ -151,8 +156,11 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         for (int w = 0; w < 2; ++w) {
             mbar_init(&bars->cl_full[w], 1); mbar_init(&bars->cl_full[w + 2], 1);
             mbar_init(&bars->cl_empty[w], 128); mbar_init(&bars->cl_empty[w + 2], 128);
-            mbar_init(&bars->s_full[w], 1); mbar_init(&bars->p_full[w], 128);
-            mbar_init(&bars->sp_free[w], 1); mbar_init(&bars->pv_done[w], 1);
+            for (int hh = 0; hh < 2; ++hh) {
+                mbar_init(&bars->s_full[2 * w + hh], 1); mbar_init(&bars->p_full[2 * w + hh], 128);
+                mbar_init(&bars->sp_free[2 * w + hh], 1);
+            }
+            mbar_init(&bars->pv_done[w], 1);
         }
         mbar_init(&bars->o_full, 1);
         mbar_init(&bars->o_free, 128);
@@ -326,7 +334,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
     } else if (warp == 2) {
         // ------------------------------------------------------------------ S-GEMM issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_s = idesc_bf16(128, kKT, 0, 0);
+            constexpr uint32_t idesc_s = idesc_bf16(128, kNS, 0, 0);
             const uint64_t q_desc = smem_desc_sw128(smem_addr(q_s), 16, 1024);
             const uint64_t a_desc0 = smem_desc_sw128(smem_addr(a_s), 16, 1024);
             int ga = 0, gc = 0, cnt[2] = {0, 0};
@@ -339,23 +347,36 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     const int w = t & 1;
                     const int idx = cnt[w]++;
                     const int gt = cnt[0] + cnt[1] - 1;
-                    if (idx >= 1 && !mbar_wait(&bars->sp_free[w], (idx - 1) & 1)) { fail(25); ok = false; break; }
+                    if (!kDense && idx >= 1 && !mbar_wait(&bars->sp_free[2 * w], (idx - 1) & 1)) { fail(25); ok = false; break; }
                     for (int us = 0; us < nu; ++us, ++ga) {
                         const int sa = ga % kAStages;
                         if (!mbar_wait(&bars->a_full[sa], (ga / kAStages) & 1)) { fail(21); ok = false; break; }
                         tc_fence_after();
                         const uint64_t ad = a_desc0 + (uint64_t)((sa * kTileBytes) >> 4);
                         const uint32_t dis = dis_mask(us);
+                        if (kDense) {
+                            for (int hh = 0; hh < 2; ++hh) {                   // keys [64 hh, 64 hh + 64) of the tile
+                                if (idx >= 1 && !mbar_wait(&bars->sp_free[2 * w + hh], (idx - 1) & 1)) { fail(25); ok = false; break; }
+                                tc_fence_after();
 #pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            const uint32_t off = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;   // same geometry for both tiles
-                            if (kDense) mma_ss(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0);
-                            else mma_ss_masked(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0, dis);
+                                for (int ks = 0; ks < 8; ++ks) {
+                                    const uint32_t off = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;
+                                    mma_ss(tmem + col_s(w) + hh * kNS, q_desc + off, ad + off + (uint32_t)((hh * kNS * 128) >> 4), idesc_s, ks > 0);
+                                }
+                                mma_commit(&bars->s_full[2 * w + hh]);
+                            }
+                            if (!ok) break;
+                        } else {
+#pragma unroll
+                            for (int ks = 0; ks < 8; ++ks) {
+                                const uint32_t off = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;   // same geometry for both tiles
+                                mma_ss_masked(tmem + col_s(w), q_desc + off, ad + off, idesc_s, ks > 0, dis);
+                            }
                         }
                         mma_commit(&bars->a_empty[sa]);
                     }
                     if (!ok) break;
-                    mma_commit(&bars->s_full[w]);
+                    if (!kDense) mma_commit(&bars->s_full[2 * w]);
                     if (t + 1 == n_tiles) mma_commit(&bars->q_empty);
                 }
             }
@@ -374,7 +395,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     const int w = t & 1;
                     const int idx = cnt[w]++;
                     const int gt = cnt[0] + cnt[1] - 1;
-                    if (!mbar_wait(&bars->p_full[w], idx & 1)) { fail(22); ok = false; break; }
+                    if (!mbar_wait(&bars->p_full[2 * w], idx & 1)) { fail(22); ok = false; break; }
                     // first GEMM of the group into this accumulator overwrites it: the previous group's
                     // result must have been read
                     if (t < 2 && gc > 0 && !mbar_wait(&bars->o_free, (gc - 1) & 1)) { fail(23); ok = false; break; }
@@ -384,19 +405,31 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                         tc_fence_after();
                         const uint64_t yd = y_desc0 + (uint64_t)((sy * kTileBytes) >> 4);
                         const uint32_t dis = dis_mask(us);
+                        if (kDense) {
+                            for (int hh = 0; hh < 2; ++hh) {                   // the tile's two 64-key halves
+                                if (hh == 1 && !mbar_wait(&bars->p_full[2 * w + 1], idx & 1)) { fail(22); ok = false; break; }
+                                tc_fence_after();
 #pragma unroll
-                        for (int kk = 0; kk < kKT / 16; ++kk) {
-                            if (kDense)
-                                mma_ts(tmem + col_o(w), tmem + col_s(w) + kk * 8, yd + ((kk * 2048) >> 4), idesc_o, (t >= 2) || (kk > 0));
-                            else
+                                for (int kk = 0; kk < kNS / 16; ++kk)
+                                    mma_ts(tmem + col_o(w), tmem + col_s(w) + hh * kNS + kk * 8,
+                                           yd + (((hh * (kNS / 16) + kk) * 2048) >> 4), idesc_o, (t >= 2) || hh > 0 || (kk > 0));
+                                mma_commit(&bars->pv_done[w]);
+                                mma_commit(&bars->sp_free[2 * w + hh]);
+                            }
+                            if (!ok) break;
+                        } else {
+#pragma unroll
+                            for (int kk = 0; kk < kKT / 16; ++kk)
                                 mma_ts_masked(tmem + col_o(w), tmem + col_s(w) + kk * 8, yd + ((kk * 2048) >> 4), idesc_o,
                                               (t >= 2) || (kk > 0), dis);
                         }
                         mma_commit(&bars->y_empty[sy]);
                     }
                     if (!ok) break;
-                    mma_commit(&bars->pv_done[w]);
-                    mma_commit(&bars->sp_free[w]);
+                    if (!kDense) {
+                        mma_commit(&bars->pv_done[w]);
+                        mma_commit(&bars->sp_free[2 * w]);
+                    }
                     if (t + 1 == n_tiles) mma_commit(&bars->o_full);
                 }
             }
@@ -408,7 +441,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
         const int row = quad * 32 + lane;
         const int us = kDense ? 0 : min(lane / R4, kMaxU - 1);       // unit slot whose bias this tile row uses
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
-        const uint32_t s_t = tmem + lane_sel + col_s(w);
+        const uint32_t s_t0 = tmem + lane_sel + col_s(w);
         const uint32_t o_t = tmem + lane_sel + col_o(w);
         const float scale_l2 = p.scale * kLog2e;
         int gc = 0, idx = 0;                  // idx: tiles this warpgroup has handled so far
@@ -417,19 +450,21 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
             const int n_tiles = group_tiles(u0, kDense ? 1 : min(U, u_end - u0));
             float m_run = -INFINITY, l_run = 0.f;
             int my_tiles = 0;
-            for (int t = w; t < n_tiles; t += 2) {
-                const int valid = min(kKT, n_keys - t * kKT);                 // keys of this tile that exist
-                if (!mbar_wait(&bars->s_full[w], idx & 1)) { fail(31); ok = false; break; }
+            for (int t = w; ok && t < n_tiles; t += 2) {
+              for (int hh = 0; hh < kH; ++hh) {                              // dense attention: the tile's two 64-key halves
+                const uint32_t s_t = s_t0 + hh * kNS;
+                const int valid = max(0, min(kNS, n_keys - t * kKT - hh * kNS));   // keys of this (half) tile that exist
+                if (!mbar_wait(&bars->s_full[2 * w + hh], idx & 1)) { fail(31); ok = false; break; }
                 const int cslot = w + 2 * (idx & 1);
                 const float* cs = bars->cl[cslot][us];
                 if (!kDense && !mbar_wait(&bars->cl_full[cslot], (idx >> 1) & 1)) { fail(33); ok = false; break; }
                 tc_fence_after();
                 // pass 1: row maximum of the biased logits (log2 units)
-                const bool tail = kDense && valid < kKT;
+                const bool tail = kDense && valid < kNS;
                 const uint64_t scale2 = f2_pack(scale_l2, scale_l2), nl2 = f2_pack(-kLog2e, -kLog2e);
                 float mx = -INFINITY;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kKT; c0 += 64) {
+                for (int c0 = 0; c0 < kNS; c0 += 64) {
                     uint32_t r[64];
                     tmem_ld64(s_t + c0, r);
                     tmem_wait_ld();
@@ -465,7 +500,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 }
                 if (__any_sync(0xffffffffu, rescale)) {
                     // the accumulator may only be touched once the previous GEMMs into it have finished
-                    if (!mbar_wait(&bars->pv_done[w], (idx - 1) & 1)) { fail(32); ok = false; break; }
+                    if (!mbar_wait(&bars->pv_done[w], (kH * idx + hh - 1) & 1)) { fail(32); ok = false; break; }
                     tc_fence_after();
 #pragma unroll 1
                     for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
@@ -483,7 +518,7 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 const uint64_t negm2 = f2_pack(neg_m, neg_m);
                 uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll 1
-                for (int c0 = 0; c0 < kKT; c0 += 32) {
+                for (int c0 = 0; c0 < kNS; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld32(s_t + c0, r);
                     tmem_wait_ld();
@@ -511,15 +546,16 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 if (!kDense) mbar_arrive(&bars->cl_empty[cslot]);
                 l_run += lsum;
                 ++my_tiles;
-                ++idx;
-                if (t + 2 >= n_tiles) {                   // this warpgroup's last tile of the group: publish (m, l)
+                if (hh == kH - 1) ++idx;
+                if (t + 2 >= n_tiles && hh == kH - 1) {   // this warpgroup's last tile of the group: publish (m, l)
                     // the previous group's statistics must have been consumed
                     if (gc > 0 && !mbar_wait(&bars->o_free, (gc - 1) & 1)) { fail(34); ok = false; break; }
                     bars->stats[w][0][row] = m_run;
                     bars->stats[w][1][row] = l_run;
                 }
                 tc_fence_before();
-                mbar_arrive(&bars->p_full[w]);
+                mbar_arrive(&bars->p_full[2 * w + hh]);
+              }
             }
         }
     } else if (warp >= 12) {
