@@ -44,8 +44,20 @@ N_LAYER_CACHES = 4                              # rotated so K/V (201 MB per lay
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each kernel at the bench
 # workload, from the ncu capture summarised in profiles/monarch_framewise_k7_ncu.md.
-NCU_TRAFFIC = {("framewise", 7): {"monarch_row_step": 267.8e6 + 566.2e6, "monarch_col_step": 624.1e6 + 13.4e6,
-                                  "layout_rope_cache_write": 43.2e6 + 4.3e6}}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of this bench at k = 7 (averaged over a
+# step's launches where the bridge budget cuts the step into several); profiles/monarch_framewise_k7_ncu.md,
+# profiles/sweep_blockings_k1_7.md and profiles/dense_k7_ncu.md give the commands
+NCU_TRAFFIC = {
+    ("framewise", 7): {"monarch_row_step": 261.1e6 + 561.3e6, "monarch_col_step": 624.0e6 + 9.4e6,
+                       "layout_rope_cache_write": 43.2e6 + 2.5e6},
+    ("tied3frame", 7): {"monarch_row_step": 216.4e6 + 157.1e6, "monarch_col_step": 217.5e6 + 6.0e6,
+                        "layout_rope_cache_write": 43.2e6 + 2.5e6},
+    ("reduce2xh", 7): {"monarch_row_step": (347.5e6 + 1123.6e6) / 2, "monarch_col_step": (1233.6e6 + 9.7e6) / 2,
+                       "layout_rope_cache_write": 43.2e6 + 3.0e6},
+    ("reduce4xw2xh", 7): {"monarch_row_step": (564.7e6 + 4543.0e6) / 6, "monarch_col_step": (4884.8e6 + 2.2e6) / 6,
+                          "layout_rope_cache_write": 43.2e6 + 2.5e6},
+    ("dense", 7): {"dense": 215.9e6 + 13.0e6},
+}
 
 
 def algorithmic(blocking: str, k: int, heads: int = HEADS, batch: int = 1):
