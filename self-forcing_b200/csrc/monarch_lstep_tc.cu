@@ -462,6 +462,46 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                 // pass 1: row maximum of the biased logits (log2 units)
                 const bool tail = kDense && valid < kNS;
                 const uint64_t scale2 = f2_pack(scale_l2, scale_l2), nl2 = f2_pack(-kLog2e, -kLog2e);
+                float lsum = 0.f;
+                bool spec_done = false;
+                if constexpr (kDense) {
+                    // After a warpgroup's first half tile the row maximum rarely moves past the rescale threshold, so
+                    // the half is first taken in ONE pass against the running reference; the packed P is only stored
+                    // if every row of the warp stayed below 2^threshold in total (then no weight exceeded it and the
+                    // two-pass path below would have produced the same bits), else the two passes run on the
+                    // untouched S.
+                    if (my_tiles > 0 && !tail) {
+                        const float nm = -m_run;
+                        const uint64_t nm2 = f2_pack(nm, nm);
+                        uint64_t ls2 = f2_pack(0.f, 0.f);
+                        uint32_t pk0[16], pk1[16];
+                        {
+                            uint32_t r[64];
+                            tmem_ld64(s_t, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int c = 0; c < 64; c += 2) {
+                                float d0, d1;
+                                f2_unpack(f2_fma(f2_pack(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, nm2), d0, d1);
+                                const float e0 = exp2f(d0), e1 = exp2f(d1);
+                                ls2 = f2_add(ls2, f2_pack(e0, e1));
+                                if (c < 32) pk0[c >> 1] = pack_bf16_alu(e0, e1);
+                                else pk1[(c - 32) >> 1] = pack_bf16_alu(e0, e1);
+                            }
+                        }
+                        float la, lb;
+                        f2_unpack(ls2, la, lb);
+                        const float ls = la + lb;
+                        if (!__any_sync(0xffffffffu, !(ls < 256.0f))) {      // 2^kRescaleThreshold; also catches inf / nan
+                            tmem_st16(s_t, pk0);
+                            tmem_st16(s_t + 16, pk1);
+                            tmem_wait_st();
+                            lsum = ls;
+                            spec_done = true;
+                        }
+                    }
+                }
+                if (!spec_done) {
                 float mx = -INFINITY;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kNS; c0 += 64) {
@@ -540,9 +580,10 @@ monarch_l_tc_kernel(const __grid_constant__ CUtensorMap tal, const __grid_consta
                     if (!lp.lse_only) tmem_st16(s_t + (c0 >> 1), pk);
                 }
                 tmem_wait_st();
-                float lsum, lsum_hi;
+                float lsum_hi;
                 f2_unpack(lsum2, lsum, lsum_hi);
                 lsum += lsum_hi;
+                }
                 if (!kDense) mbar_arrive(&bars->cl_empty[cslot]);
                 l_run += lsum;
                 ++my_tiles;
