@@ -301,6 +301,30 @@ def test_dense_attention_vs_reference_fixture(sfb, i):
     check_close(got, torch.from_numpy(pins[f"dense_{i}_fp32"]), f"dense case {i}")
 
 
+@pytest.mark.parametrize("gain", [0.02, 0.2, 1.0, 3.0])
+def test_dense_attention_with_a_growing_maximum(sfb, gain):
+    """Keys ordered so that every query's logits rise along the cache, by about 0.2, 2, 10 and 31 in log2 units per
+    64 keys.  The slowest rise stays inside the rescale threshold of 8 for long stretches (half tiles taken in the
+    speculative single pass against a reference that falls behind), the second passes it every few half tiles (the
+    row sums refuse the speculative pass and the two-pass path rescales the accumulator), the last two at every
+    half tile."""
+    rng = np.random.default_rng(77)
+    B, H, D, n_q, n_kv = 1, 2, 128, 256, 1500
+    q = cases.randn(rng, B, n_q, H, D)
+    direction = q.mean(dim=1, keepdim=True)
+    direction = direction / direction.norm(dim=-1, keepdim=True)
+    ramp = torch.linspace(0.0, 1.0, n_kv).view(1, n_kv, 1, 1)
+    k = 0.3 * cases.randn(rng, B, n_kv, H, D) + gain * 400.0 * ramp * direction
+    v = cases.randn(rng, B, n_kv, H, D)
+    q = q + 4.0 * direction                                   # every query has a solid component along the ramp
+    q, k, v = bf(q), bf(k), bf(v)
+    got = sfb.attention(q.cuda(), k.cuda(), v.cuda())
+    ref = orc.dense_attention(q.float(), k.float(), v.float())
+    check_close(got, ref, f"dense, rising logits (gain {gain})")
+    ops_mod = __import__("self_forcing_b200").ops
+    ops_mod.check_device_status()
+
+
 def test_dense_with_cache_write(sfb):
     rng = np.random.default_rng(8)
     B, H, D, n = 1, 2, 128, 96
