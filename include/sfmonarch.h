@@ -313,9 +313,12 @@ int sfm_monarch_fwd_scatter(const void* q, int64_t q_batch_stride,
  *            the backward of the no-cache call, with k_cache / v_cache = its k_mon / v_mon
  *   workspace  sfm_monarch_bwd_workspace_bytes(...) bytes; the call is cut into slices of
  *            (batch, head) pairs whose scratch stays under budget_bytes (0 = 2 GiB)
- * The three kernels recompute the row step in fp32, so nothing has to be saved by the forward
- * call; dq is accumulated without atomics (results are run-to-run identical).  Block rows and
- * block columns up to 128.
+ * Nothing has to be saved by the forward call: the backward recomputes the row step (and the column
+ * step's softmax statistics) itself, then runs the column-step and the row-step backward; dq, dk and dv
+ * are accumulated without atomics (results are run-to-run identical).  Block rows and block columns
+ * up to 128.  Without a mask, for block rows up to 96 and block columns up to 64, all of it runs on
+ * the tensor cores with aL, Y and their gradients in bf16 (as in the reference); other shapes run
+ * fp32 kernels.  The first word of the workspace is the call's status word (sfm_workspace_status).
  * Replaces: _attention_with_cache.backward (wan/modules/monarch_attn.py:1325-1470) and its
  * kernels (:403-596, 1034-1222), and _attention_no_cache.backward (:1565-1694).
  */
