@@ -36,7 +36,7 @@ using namespace tc;
 
 namespace {
 
-constexpr int kStages = 5;            // K/V tile ring
+constexpr int kStages = 8;            // K/V tile ring, at most (128 KB: 2 x 64 KB, 4 x 32 KB or 8 x 16 KB stages by block width)
 constexpr int kThreads = 608;          // 19 warps: one more would lower the register ceiling from 104 to 96
 constexpr int kTileRows = 128;
 constexpr uint32_t kTmemCols = 512;
@@ -91,7 +91,7 @@ struct __align__(8) Barriers {
 // shared memory carve-up (bytes from a 1024-aligned base)
 constexpr int kQBytes = 2 * kTileRows * 128;               // two 64-column halves
 constexpr int kStageBytes = 4 * 64 * 128;                  // K half 0, K half 1, V half 0, V half 1 (<= 64 rows each)
-constexpr int kSmemBytes = 1024 + kQBytes + kStages * kStageBytes + 256;
+constexpr int kSmemBytes = 1024 + 2 * kQBytes + 4 * kStageBytes + 256;   // two query tiles, 128 KB of K / V stages
 
 // 32-byte store of 16 bf16 to global memory (pointer 32-byte aligned).
 __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
@@ -111,8 +111,8 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
-    unsigned char* kv_s = q_s + (kIter ? 2 : 1) * kQBytes;
-    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + (N_S > 64 ? 2 * 2 * kStageBytes : (kIter ? kStages - 1 : kStages) * kStageBytes));
+    unsigned char* kv_s = q_s + 2 * kQBytes;                 // two query tiles: the next unit's loads while this one is worked on
+    Barriers* bars = reinterpret_cast<Barriers*>(kv_s + 4 * kStageBytes);
 
     const MonarchParams& p = rp.mp;
     const Blocking& blk = p.blk;
@@ -123,9 +123,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     // Block columns above 64 (wide grids): 128-row K / V stages (two of them fit), S/P buffers and the
     // accumulator move up in TMEM, and the softmax walks its row in 32-column chunks (see below).
     constexpr bool kWide = N_S > 64;
-    constexpr int kStg = kWide ? 2 : (kIter ? kStages - 1 : kStages);
-    constexpr int kStgBytes = kWide ? 2 * kStageBytes : kStageBytes;
+    // a stage holds K lo, K hi, V lo, V hi of N_S rows each: 16 KB up to 32 block columns, 32 KB up to 64, 64 KB beyond
+    constexpr int kStg = kWide ? 2 : (N_S <= 32 ? 8 : 4);
+    constexpr int kStgBytes = kWide ? 2 * kStageBytes : (N_S <= 32 ? kStageBytes / 2 : kStageBytes);
     constexpr uint32_t cS1 = kWide ? 128u : kColS1, cO = kWide ? 256u : kColO;
+    // Single pass: the next unit's query tile loads into the other buffer while this unit is worked on (short units
+    // at small cache lengths otherwise wait for it); measured slower for narrow blocks (up to 32 columns), which keep one.
+    constexpr bool kQDouble = kIter || N_S > 32;
+    constexpr int kQBufs = kQDouble ? 2 : 1;
 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); }
@@ -161,12 +166,14 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 const int g_first = un.tile * rp.groups_per_tile;
                 const int ng = min(rp.groups_per_tile, p.na - g_first);
                 if constexpr (!kIter) {
-                    if (uc > 0 && !mbar_wait(&bars->q_empty[0], (uc - 1) & 1)) { fail(10); break; }
-                    mbar_arrive_expect_tx(&bars->q_full[0], (uint32_t)(ng * RG * 256));
+                    const int qb = kQDouble ? (uc & 1) : 0;
+                    unsigned char* qd = q_s + qb * kQBytes;
+                    if (uc >= kQBufs && !mbar_wait(&bars->q_empty[qb], ((uc / kQBufs) - 1) & 1)) { fail(10); break; }
+                    mbar_arrive_expect_tx(&bars->q_full[qb], (uint32_t)(ng * RG * 256));
                     for (int gi = 0; gi < ng; ++gi) {
                         int tok = blk.row_token(p.a0 + g_first + gi, un.k);
-                        tma_load_4d(q_s + gi * RG * 128, &tq, &bars->q_full[0], 0, hd, tok, b);
-                        tma_load_4d(q_s + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full[0], 64, hd, tok, b);
+                        tma_load_4d(qd + gi * RG * 128, &tq, &bars->q_full[qb], 0, hd, tok, b);
+                        tma_load_4d(qd + kTileRows * 128 + gi * RG * 128, &tq, &bars->q_full[qb], 64, hd, tok, b);
                     }
                 }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
@@ -209,7 +216,7 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                 const RUnit un = decode_unit<kCausal>(rp, u);
                 if (kCausal && un.n_it == 0) continue;
                 if constexpr (!kIter) {
-                    if (!mbar_wait(&bars->q_full[0], uc & 1)) { fail(20); break; }
+                    if (!mbar_wait(&bars->q_full[kQDouble ? (uc & 1) : 0], (uc / kQBufs) & 1)) { fail(20); break; }
                 }
                 for (int i = 0; i < un.n_it; ++i, ++g) {
                     const int s = g % kStg;
@@ -225,13 +232,13 @@ monarch_r_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     for (int ks = 0; ks < 8; ++ks) {
                         const uint32_t q_off = ((ks >> 2) * (kTileRows * 128) + (ks & 3) * 32) >> 4;
                         const uint32_t k_off = ((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-                        mma_ss(d, q_desc + (kIter ? (uint32_t)(((g & 1) * kQBytes) >> 4) : 0u) + q_off, kd + k_off, idesc_s, ks > 0);
+                        mma_ss(d, q_desc + (uint32_t)((((kIter ? g : (kQDouble ? uc : 0)) & 1) * kQBytes) >> 4) + q_off, kd + k_off, idesc_s, ks > 0);
                     }
                     mma_commit(&bars->s_full[g & 1]);
                     if constexpr (kIter) {
                         mma_commit(&bars->q_empty[g & 1]);                 // this step's query tile has been read
                     } else {
-                        if (i + 1 == un.n_it) mma_commit(&bars->q_empty[0]);   // last read of this unit's Q tile
+                        if (i + 1 == un.n_it) mma_commit(&bars->q_empty[kQDouble ? (uc & 1) : 0]);   // last read of this unit's Q tile
                     }
                 }
                 ++uc;
@@ -516,8 +523,7 @@ int launch_r_step_tc(const MonarchParams& p, const CUtensorMap* maps /* q (or th
     // wide blocks: two 64 KB K / V stages instead of five 32 KB ones
     const bool iter = p.use_aR != 0;
     if (iter && (n_s > 64 || p.causal_groups > 0)) return SFM_ERR_UNSUPPORTED;
-    const int smem_bytes = n_s > 64 ? 1024 + kQBytes + 2 * 2 * kStageBytes + 256
-                                    : (iter ? 1024 + 2 * kQBytes + (kStages - 1) * kStageBytes + 256 : kSmemBytes);
+    const int smem_bytes = kSmemBytes;
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return (int)e;
